@@ -1,6 +1,6 @@
 from .manager import FREED, AppendPlan, CacheManager, EntryCache, RequestCache, token_bytes
-from .needs import FixedState, PagedKV
+from .needs import FixedState, PagedKV, PagedLatent
 from .pages import OutOfPages, PagePool
 
 __all__ = ["FREED", "AppendPlan", "CacheManager", "EntryCache", "RequestCache", "FixedState",
-           "PagedKV", "OutOfPages", "PagePool", "token_bytes"]
+           "PagedKV", "PagedLatent", "OutOfPages", "PagePool", "token_bytes"]

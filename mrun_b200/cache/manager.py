@@ -25,7 +25,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 
 from . import native
-from .needs import FixedState, PagedKV
+from .needs import FixedState, PagedKV, PagedLatent
 from .pages import OutOfPages
 
 FREED = -1  # block-table entry of a logical block whose page was given back (or never taken)
@@ -129,6 +129,8 @@ def token_bytes(needs: Sequence[object], shares: Sequence[Optional[int]], elemen
             continue
         if isinstance(need, PagedKV):
             per_token += 2 * need.kv_heads * need.head_dim * element_size
+        elif isinstance(need, PagedLatent):
+            per_token += need.width * element_size
         elif isinstance(need, FixedState):
             count = 1
             for extent in need.shape:
@@ -171,7 +173,7 @@ class CacheManager:
                 continue
             if need is None:
                 self.entries.append(None)
-            elif isinstance(need, PagedKV):
+            elif isinstance(need, (PagedKV, PagedLatent)):
                 if need.window is not None and need.window < 1:
                     raise ValueError(f"schedule entry {i}: window must be at least 1, got {need.window}")
                 key = need.group_key()
@@ -186,9 +188,12 @@ class CacheManager:
                 k = v = None
                 if device is not None:
                     import torch
-                    shape = (num_pages, need.kv_heads, page_size, need.head_dim)
-                    k = torch.zeros(shape, dtype=dtype, device=device)
-                    v = torch.zeros(shape, dtype=dtype, device=device)
+                    if isinstance(need, PagedLatent):       # one row a token: the key and the value
+                        k = v = torch.zeros((num_pages, 1, page_size, need.width), dtype=dtype, device=device)
+                    else:
+                        shape = (num_pages, need.kv_heads, page_size, need.head_dim)
+                        k = torch.zeros(shape, dtype=dtype, device=device)
+                        v = torch.zeros(shape, dtype=dtype, device=device)
                 self.entries.append(EntryCache(need, key, True, k=k, v=v))
             elif isinstance(need, FixedState):
                 state = None
@@ -246,8 +251,8 @@ class CacheManager:
     def bytes_per_page(self) -> int:
         total = 0
         for entry in self.entries:
-            if entry is not None and entry.writable and isinstance(entry.need, PagedKV) and entry.k is not None:
-                total += 2 * entry.k[0].numel() * entry.k.element_size()
+            if entry is not None and entry.writable and isinstance(entry.need, (PagedKV, PagedLatent)) and entry.k is not None:
+                total += (1 if entry.v is entry.k else 2) * entry.k[0].numel() * entry.k.element_size()
         return total
 
     # ------------------------------------------------------------------ requests

@@ -25,6 +25,20 @@ class PagedKV:
 
 
 @dataclass(frozen=True)
+class PagedLatent:
+    """One row of ``width`` features per token that serves as the key and as the value of a
+    single key/value head (an attention over a shared latent): one tensor of pages, which the
+    entry's ``k`` and ``v`` both name.  Shares the pages' books with :class:`PagedKV` of the same
+    window."""
+
+    width: int
+    window: Optional[int] = None
+
+    def group_key(self) -> tuple:
+        return ("paged", self.window)
+
+
+@dataclass(frozen=True)
 class FixedState:
     """Per-request state of a fixed shape, zero when a request starts."""
 

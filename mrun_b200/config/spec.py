@@ -38,9 +38,13 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class RMSNormSpec:
+    """``bare``: the checkpoint names the scale vector by the norm's own name, without a
+    ``.weight`` after it."""
+
     kind: ClassVar[str] = "rmsnorm"
     size: int
     eps: float
+    bare: bool = False
 
 
 # --------------------------------------------------------------------------- position encodings
@@ -53,6 +57,25 @@ class RotarySpec:
     head_dim: int
     rotary_dim: int
     theta: float
+
+
+@dataclass(frozen=True)
+class ScaledRotarySpec:
+    """Rotary positions over the first ``dims`` features of a vector, with a choice of pairing
+    (``"interleaved"``: feature 2i with 2i + 1; ``"half"``: i with i + dims/2) and an optional
+    band-wise stretch of the frequencies (``scaling`` = (factor, original, fast, slow)).
+
+    Pair i has the frequency f_i = base^(-2i/dims).  With a stretch: d(t) = dims * ln(original /
+    (2 pi t)) / (2 ln base) is the (fractional) pair that makes t turns over ``original``
+    positions; lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), dims - 1), r_i = clamp((i - lo)
+    / max(hi - lo, 0.001), 0, 1); the frequency becomes f_i / factor * r_i + f_i * (1 - r_i), and
+    cos and sin are both multiplied by 0.1 * ln(factor) + 1."""
+
+    kind: ClassVar[str] = "rotary_scaled"
+    dims: int
+    base: float
+    pairing: str = "interleaved"
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 # --------------------------------------------------------------------------- mixers
@@ -76,6 +99,30 @@ class AttentionSpec:
     window: Optional[int] = None
 
 
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values are up-projections of one cached latent per token.
+
+    Per token: the query goes through a latent of ``q_rank`` features (RMS-normed), then up to
+    ``heads`` heads of ``dim`` plain and ``rot_dim`` rotated features.  One down-projection gives
+    the key/value latent of ``kv_rank`` features (RMS-normed) and ``rot_dim`` more that are the
+    rotated key part all heads share.  A head's plain key is an up-projection of the latent, its
+    value (``vdim`` features) another; the score is (plain . plain + rotated . rotated) *
+    ``softmax_scale``.  The cache holds the latent and the shared rotated part only."""
+
+    kind: ClassVar[str] = "latent_attention"
+    hidden: int
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    softmax_scale: float
+    eps: float
+    position: Optional[Any] = None
+
+
 # --------------------------------------------------------------------------- feed-forwards
 
 @dataclass(frozen=True)
@@ -86,13 +133,48 @@ class GatedMLPSpec:
     hidden: int
     intermediate: int
     activation: str = "silu"
+    # the checkpoint's names of the gate, up and down matrices under the part's prefix; a name
+    # that ends in ``.weight`` may have a ``.bias`` beside it
+    tensor_names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """A mixture of ``experts`` small feed-forwards ``down(act(up(x)))`` without biases, of which
+    each token takes the ``top`` with the largest router scores, plus an optional shared expert
+    of the same form that every token takes.  ``score``: ``"softmax"`` over all experts or
+    ``"sigmoid"`` of each logit, in 32-bit; ``renormalize``: whether the chosen scores are divided
+    by their sum before they weigh the experts' outputs."""
+
+    kind: ClassVar[str] = "routed_mlp"
+    hidden: int
+    experts: int
+    top: int
+    expert_ff: int
+    shared_ff: int = 0
+    activation: str = "relu2"
+    score: str = "softmax"
+    renormalize: bool = False
+
+
+# --------------------------------------------------------------------------- transforms
+
+@dataclass(frozen=True)
+class SoftCapSpec:
+    """x -> cap * tanh(x / cap)."""
+
+    kind: ClassVar[str] = "soft_cap"
+    cap: float
 
 
 # --------------------------------------------------------------------------- layers and model
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: norm → mixer → residual → norm → feed-forward → residual (``pre_norm``)."""
+    """One block: norm → mixer → residual → norm → feed-forward → residual (``pre_norm``).  The
+    ``sandwich`` arrangement also norms each branch's output (``*_post_norm``) and multiplies it
+    by ``residual_scale`` before the sum; its ``feed_forward`` may be None (a layer of a mixer
+    only)."""
 
     prefix: str
     mixer: Any
@@ -104,6 +186,11 @@ class LayerSpec:
     feed_forward_prefix: str = "mlp"
     mixer_norm_prefix: str = "input_layernorm"
     feed_forward_norm_prefix: str = "post_attention_layernorm"
+    mixer_post_norm: Any = None
+    feed_forward_post_norm: Any = None
+    mixer_post_norm_prefix: str = "post_mixer_norm"
+    feed_forward_post_norm_prefix: str = "post_feed_forward_norm"
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)

@@ -190,11 +190,12 @@ MRUN_API int mrun_add_rmsnorm(float* resid, const void* delta, const float* weig
 // ------------------------------------------------------------------------------------------
 // Rotation table: out[t, j] = (cos a, sin a), a = position[t] * inv_freq[j], the product and the
 // functions in 64-bit, rounded once (the reference's explicit form computes the angle in
-// 64-bit too, crates/mrun-engine/src/models/common.rs:264-270).  A negative position (padding)
-// gives (1, 0).
+// 64-bit too, crates/mrun-engine/src/models/common.rs:264-270).  Both are multiplied by
+// `magnitude` (1 for plain rotary positions; a scaled encoding may lengthen the rotated vector).
+// A negative position (padding) gives (1, 0).
 // ------------------------------------------------------------------------------------------
 __global__ void rotary_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                    float2* __restrict__ out, int tokens, int half) {
+                                    float2* __restrict__ out, int tokens, int half, double magnitude) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= tokens * half) return;
     const int t = i / half, j = i - t * half;
@@ -205,15 +206,15 @@ __global__ void rotary_table_kernel(const int* __restrict__ positions, const dou
     }
     double s, c;
     sincos((double)p * inv_freq[j], &s, &c);
-    out[i] = make_float2((float)c, (float)s);
+    out[i] = make_float2((float)(c * magnitude), (float)(s * magnitude));
 }
 
 MRUN_API int mrun_rotary_table(const int* positions, const double* inv_freq, float* out, int tokens,
-                               int half, cudaStream_t stream) {
+                               int half, double magnitude, cudaStream_t stream) {
     MRUN_REQUIRE(tokens >= 0 && half > 0, "rotary_table: bad sizes tokens=%d half=%d", tokens, half);
     if (tokens == 0) return 0;
     const int n = tokens * half;
-    rotary_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)out, tokens, half);
+    rotary_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)out, tokens, half, magnitude);
     MRUN_CHECK_LAUNCH("rotary_table");
     return 0;
 }

@@ -13,7 +13,10 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 __global__ void __launch_bounds__(256)
 gemm_f32_nt_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int M,
-                   int N, int K, long ldx, long ldy) {
+                   int N, int K, long ldx, long ldy, long batch_x, long batch_w, long batch_y) {
+    x += blockIdx.z * batch_x;
+    w += blockIdx.z * batch_w;
+    y += blockIdx.z * batch_y;
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -74,7 +77,25 @@ MRUN_API int mrun_gemm_f32_nt(const float* x, const float* w, float* y, int M, i
     if (M == 0) return 0;
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     MRUN_REQUIRE(grid.y <= 65535, "gemm_f32_nt: M=%d exceeds the supported %d rows", M, 65535 * BM);
-    gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldy);
+    gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldy, 0, 0, 0);
     MRUN_CHECK_LAUNCH("gemm_f32_nt");
+    return 0;
+}
+
+// The same product for `batch` independent problems (the heads of a per-head projection): problem b
+// reads x + b * batch_x (rows ldx apart) and the dense w + b * batch_w [N, K], and writes
+// y + b * batch_y (rows ldy apart).  The sum over k keeps its fixed order.
+MRUN_API int mrun_gemm_f32_nt_batched(const float* x, const float* w, float* y, int batch, int M, int N, int K,
+                                      long ldx, long ldy, long batch_x, long batch_w, long batch_y,
+                                      cudaStream_t stream) {
+    MRUN_REQUIRE(batch > 0 && batch <= 65535 && M >= 0 && N > 0 && K > 0,
+                 "gemm_f32_nt_batched: bad sizes batch=%d M=%d N=%d K=%d", batch, M, N, K);
+    MRUN_REQUIRE(ldx >= K && ldy >= N, "gemm_f32_nt_batched: row strides ldx=%ld ldy=%ld below K=%d N=%d", ldx,
+                 ldy, K, N);
+    if (M == 0) return 0;
+    const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    MRUN_REQUIRE(grid.y <= 65535, "gemm_f32_nt_batched: M=%d exceeds the supported %d rows", M, 65535 * BM);
+    gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldy, batch_x, batch_w, batch_y);
+    MRUN_CHECK_LAUNCH("gemm_f32_nt_batched");
     return 0;
 }

@@ -99,14 +99,14 @@ class Model:
         delta = None
         for at, entry in enumerate(self.order):
             block = self.blocks[entry.layer]
-            if isinstance(delta, ops.PendingLinear) and not getattr(block, "accepts_pending", False):
+            if isinstance(delta, ops.PENDING) and not getattr(block, "accepts_pending", False):
                 delta = delta.compute()
             delta = block.forward(resid, delta, ctx, caches[at])
         return resid, delta
 
     def logits(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """float32 ``[len(rows), vocab]``: final norm and head at the wanted rows only."""
-        if isinstance(delta, ops.PendingLinear):
+        if isinstance(delta, ops.PENDING) and not getattr(self.final_norm, "accepts_pending", False):
             delta = delta.compute()
         h = self.final_norm.rows_forward(resid, delta, rows)
         logits = ops.linear(h, self.head, out_dtype=torch.float32)

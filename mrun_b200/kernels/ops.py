@@ -74,15 +74,16 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     return out
 
 
-def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, j] = (cos, sin)(positions[t] * inv_freq[j]); inv_freq is float64."""
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor,
+                 magnitude: float = 1.0) -> torch.Tensor:
+    """out[t, j] = magnitude * (cos, sin)(positions[t] * inv_freq[j]); inv_freq is float64."""
     _check(positions, "positions", torch.int32); _check(inv_freq, "inv_freq", torch.float64)
     _check(out, "out", torch.float32)
     tokens, half = positions.numel(), inv_freq.numel()
     if out.shape != (tokens, half, 2):
         raise KernelError(f"rotary_table: out is {tuple(out.shape)}, expected {(tokens, half, 2)}")
     _lib.core().call("mrun_rotary_table", _ptr(positions), _ptr(inv_freq), _ptr(out), _c_int(tokens),
-                     _c_int(half), _stream())
+                     _c_int(half), ctypes.c_double(magnitude), _stream())
     return out
 
 
@@ -271,6 +272,27 @@ class PendingLinear:
 
     def compute(self) -> torch.Tensor:
         return linear(self.x, self.w)
+
+
+class PendingPostNorm:
+    """A branch output (float32 rows) that joins the stream as ``scale * rmsnorm(branch) * weight``
+    and has not been added yet: the norm that follows adds it and norms the new rows in one
+    kernel (:func:`post_norm_add`).  :meth:`compute` makes the addend itself."""
+
+    def __init__(self, branch: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, act: torch.dtype):
+        self.branch, self.weight, self.eps, self.scale, self.act = branch, weight, float(eps), float(scale), act
+
+    @property
+    def shape(self):
+        return self.branch.shape
+
+    def compute(self) -> torch.Tensor:
+        addend = torch.zeros_like(self.branch)
+        post_norm_add(addend, self.branch, self.weight, self.scale, self.eps, None, 0.0, None)
+        return addend.to(self.act)
+
+
+PENDING = (PendingLinear, PendingPostNorm)      # what a block may hand to the norm after it unadded
 
 
 def _normed(x):
@@ -557,3 +579,158 @@ def select_tokens(ids: torch.Tensor, previous: torch.Tensor, source: torch.Tenso
     _lib.core().call("mrun_select_tokens", _ptr(ids), _ptr(previous), _ptr(source), _c_int(ids.numel()),
                      _c_int(previous.numel()), _stream())
 
+
+
+# ------------------------------------------------------------------ latent attention, sandwich norms, routing
+
+def gemm_f32_nt_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = x[b] @ w[b].T in IEEE 32-bit with a fixed summation order.  ``x`` [batch, M, K] and
+    ``out`` [batch, M, N] may be strided views (unit stride along the last axis: the heads of a
+    row laid side by side); ``w`` is dense [batch, N, K]."""
+    _check(x, "x", torch.float32, dense=False); _check(w, "w", torch.float32); _check(out, "out", torch.float32, dense=False)
+    batch, m, k = x.shape
+    n = w.shape[1]
+    if w.shape != (batch, n, k) or out.shape != (batch, m, n) or x.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError(f"gemm_f32_nt_batched: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    _lib.core().call("mrun_gemm_f32_nt_batched", _ptr(x), _ptr(w), _ptr(out), _c_int(batch), _c_int(m), _c_int(n),
+                     _c_int(k), _c_long(x.stride(1) if m > 1 else max(k, x.stride(1))),
+                     _c_long(out.stride(1) if m > 1 else max(n, out.stride(1))),
+                     _c_long(x.stride(0)), _c_long(n * k), _c_long(out.stride(0)), _stream())
+    return out
+
+
+def linear_per_head(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[:, h] = x[:, h] @ w[h].T for every head h: ``x`` [tokens, heads, K] and ``out``
+    [tokens, heads, N] may be views into wider rows, ``w`` is dense [heads, N, K].  float32: this
+    library's IEEE kernel; bfloat16: the vendor library's batched product with 32-bit sums."""
+    if x.dtype == torch.float32:
+        gemm_f32_nt_batched(x.transpose(0, 1), w, out.transpose(0, 1))
+    else:
+        _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
+        torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    return out
+
+
+PAIRINGS = {"half": 0, "interleaved": 1}     # which features a rotation pairs: (i, i + n/2) or (2i, 2i + 1)
+
+
+def latent_prepare(down: torch.Tensor, q_weight: Optional[torch.Tensor], kv_weight: torch.Tensor, eps: float,
+                   rot: Optional[torch.Tensor], rot_dims: int, pairing: str, slots: Optional[torch.Tensor],
+                   cq: Optional[torch.Tensor], cache: Optional[torch.Tensor], q_rank: int, kv_rank: int,
+                   rot_dim: int) -> None:
+    """Rows of ``down`` = [query latent | key/value latent | shared key part].  ``cq`` gets the
+    normed query latent; the token's row of ``cache`` ([pages, 1, page_size, width], named by
+    ``slots``) gets [normed key/value latent | shared key part, its first ``rot_dims`` features
+    rotated | zeros]."""
+    _check(down, "down", dense=False)
+    tokens = down.shape[0]
+    if down.dim() != 2 or down.stride(1) != 1 or down.shape[1] != q_rank + kv_rank + rot_dim:
+        raise KernelError(f"latent_prepare: down is {tuple(down.shape)}, expected width {q_rank + kv_rank + rot_dim}")
+    _check(kv_weight, "kv_weight", torch.float32)
+    if kv_weight.numel() != kv_rank:
+        raise KernelError("latent_prepare: the key/value norm weight does not have kv_rank elements")
+    if q_rank:
+        _check(q_weight, "q_weight", torch.float32); _check(cq, "cq", down.dtype)
+        if q_weight.numel() != q_rank or cq.shape != (tokens, q_rank):
+            raise KernelError("latent_prepare: the query latent's weight or output does not have q_rank columns")
+    width = kv_rank + rot_dim
+    if slots is not None:
+        _check(slots, "slots", torch.int32); _check(cache, "cache", down.dtype)
+        if slots.numel() != tokens or cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] < width:
+            raise KernelError(f"latent_prepare: cache is {tuple(cache.shape)}, expected [pages, 1, page_size, >= {width}]")
+        width = cache.shape[3]
+    if rot_dims:
+        _check(rot, "rot", torch.float32)
+        if rot.shape != (tokens, rot_dims // 2, 2):
+            raise KernelError(f"latent_prepare: rot is {tuple(rot.shape)}, expected {(tokens, rot_dims // 2, 2)}")
+    _lib.core().call("mrun_latent_prepare", _ptr(down), dtype_code(down.dtype), _c_long(down.stride(0)),
+                     _ptr(q_weight), _ptr(kv_weight), _c_float(eps), _ptr(rot), _c_int(rot_dims),
+                     _c_int(PAIRINGS[pairing]), _ptr(slots), _ptr(cq), _ptr(cache if slots is not None else None),
+                     _c_int(tokens), _c_int(q_rank), _c_int(kv_rank), _c_int(rot_dim), _c_int(width), _stream())
+
+
+def latent_query(q: torch.Tensor, rot: Optional[torch.Tensor], rot_dims: int, pairing: str, q_att: torch.Tensor,
+                 heads: int, dim: int, rot_dim: int, kv_rank: int) -> None:
+    """``q`` [tokens, heads * (dim + rot_dim)]; fills ``q_att[t, h, kv_rank:]`` with the head's
+    rotated part and zeros ([tokens, heads, width])."""
+    _check(q, "q"); _check(q_att, "q_att", q.dtype)
+    tokens = q.shape[0]
+    if q.shape != (tokens, heads * (dim + rot_dim)) or q_att.dim() != 3 or q_att.shape[:2] != (tokens, heads) \
+            or q_att.shape[2] < kv_rank + rot_dim:
+        raise KernelError(f"latent_query: q {tuple(q.shape)}, q_att {tuple(q_att.shape)}")
+    if rot_dims:
+        _check(rot, "rot", torch.float32)
+        if rot.shape != (tokens, rot_dims // 2, 2):
+            raise KernelError(f"latent_query: rot is {tuple(rot.shape)}, expected {(tokens, rot_dims // 2, 2)}")
+    _lib.core().call("mrun_latent_query", _ptr(q), dtype_code(q.dtype), _ptr(rot), _c_int(rot_dims),
+                     _c_int(PAIRINGS[pairing]), _ptr(q_att), _c_int(tokens), _c_int(heads), _c_int(dim),
+                     _c_int(rot_dim), _c_int(kv_rank), _c_int(q_att.shape[2]), _stream())
+
+
+def post_norm_add(stream: torch.Tensor, branch: torch.Tensor, w_post: torch.Tensor, scale: float, eps_post: float,
+                  w_next: Optional[torch.Tensor], eps_next: float, out: Optional[torch.Tensor],
+                  rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """stream += scale * rmsnorm(branch) * w_post (32-bit, in place), then out = rmsnorm(stream) *
+    w_next (skipped when ``w_next`` is None).  With ``rows`` only those rows are computed and the
+    stream is left as it is.  ``branch`` is float32."""
+    _check(stream, "stream", torch.float32); _check(branch, "branch", torch.float32)
+    _check(w_post, "w_post", torch.float32)
+    hidden = stream.shape[1]
+    n_rows = stream.shape[0] if rows is None else rows.numel()
+    if branch.shape != stream.shape or w_post.numel() != hidden:
+        raise KernelError(f"post_norm_add: stream {tuple(stream.shape)}, branch {tuple(branch.shape)}, weight {w_post.numel()}")
+    code = F32
+    if w_next is not None:
+        _check(w_next, "w_next", torch.float32); _check(out, "out")
+        if w_next.numel() != hidden or out.shape != (n_rows, hidden):
+            raise KernelError(f"post_norm_add: out {tuple(out.shape)}, expected {(n_rows, hidden)}")
+        code = dtype_code(out.dtype)
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    _lib.core().call("mrun_post_norm_add", _ptr(stream), _ptr(branch), _ptr(w_post), _c_float(scale),
+                     _c_float(eps_post), _ptr(w_next), _c_float(eps_next), _ptr(out if w_next is not None else None),
+                     _c_int(code), _ptr(rows), _c_int(n_rows), _c_int(hidden), _stream())
+    return out
+
+
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def route_top_k(logits: torch.Tensor, top: int, score: str = "softmax", renormalize: bool = False,
+                chosen: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [tokens, experts]: each token's ``top`` largest scores at their experts' places
+    (divided by their sum if ``renormalize``), zero elsewhere."""
+    _check(logits, "logits", torch.float32)
+    tokens, experts = logits.shape
+    weights = torch.empty_like(logits)
+    if chosen is not None:
+        _check(chosen, "chosen", torch.int32)
+        if chosen.shape != (tokens, top):
+            raise KernelError(f"route_top_k: chosen is {tuple(chosen.shape)}, expected {(tokens, top)}")
+    _lib.core().call("mrun_route_top_k", _ptr(logits), _ptr(weights), _ptr(chosen), _c_int(tokens), _c_int(experts),
+                     _c_int(top), _c_int(ROUTER_SCORES[score]), _c_int(1 if renormalize else 0), _stream())
+    return weights
+
+
+def relu2_scaled(u: torch.Tensor, weights: Optional[torch.Tensor], experts: int, ff: int) -> torch.Tensor:
+    """relu(u)^2 column by column; column c < experts * ff is also multiplied by
+    ``weights[t, c // ff]`` (float32 [tokens, experts]); later columns are not."""
+    _check(u, "u")
+    tokens, columns = u.shape
+    if weights is not None:
+        _check(weights, "weights", torch.float32)
+        if weights.shape != (tokens, experts):
+            raise KernelError(f"relu2_scaled: weights {tuple(weights.shape)}, expected {(tokens, experts)}")
+    else:
+        experts = 0
+    act = torch.empty_like(u)
+    _lib.core().call("mrun_relu2_scaled", _ptr(u), _ptr(act), dtype_code(u.dtype), _ptr(weights), _c_int(tokens),
+                     _c_int(columns), _c_int(experts), _c_int(max(1, ff)), _stream())
+    return act
+
+
+def soft_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place on float32."""
+    _check(x, "x", torch.float32)
+    _lib.core().call("mrun_soft_cap", _ptr(x), _c_long(x.numel()), _c_float(cap), _stream())
+    return x

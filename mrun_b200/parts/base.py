@@ -16,7 +16,7 @@ norm            ``forward(x) -> y``; ``add_forward(resid, delta) -> y`` adds ``d
 position        ``rotary_dim`` and ``rotation(ctx) -> float32 [tokens, rotary_dim // 2, 2]``
                 (cos, sin) per token and pair (j, j + rotary_dim // 2), computed once per step
                 and shared by all layers through ``ctx.shared``.
-mixer           ``cache_need() -> PagedKV | FixedState | None`` and
+mixer           ``cache_need() -> PagedKV | PagedLatent | FixedState | None`` and
                 ``forward(x, ctx, cache) -> y`` with x, y ``[tokens, hidden]`` in the activation
                 dtype; ``cache`` is the schedule entry's :class:`EntryCache`
                 (``writable`` False when it reads another entry's cache).
@@ -120,6 +120,10 @@ register_transform = TRANSFORMS.register
 
 
 def local(tensors: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:
-    """The tensors under ``prefix.`` with the prefix removed."""
+    """The tensors under ``prefix.`` with the prefix removed; a tensor named ``prefix`` itself
+    comes under the empty name."""
     dot = prefix + "."
-    return {name[len(dot):]: t for name, t in tensors.items() if name.startswith(dot)}
+    out = {name[len(dot):]: t for name, t in tensors.items() if name.startswith(dot)}
+    if prefix in tensors:
+        out[""] = tensors[prefix]
+    return out

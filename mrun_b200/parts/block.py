@@ -25,7 +25,7 @@ from .base import FEED_FORWARDS, MIXERS, NORMS, Runtime, local, register_arrange
 def norm_add(norm, resid: torch.Tensor, delta):
     """``norm.add_forward`` for a ``delta`` that may be pending: computed first unless the norm
     takes it as it is."""
-    if isinstance(delta, ops.PendingLinear) and not getattr(norm, "accepts_pending", False):
+    if isinstance(delta, ops.PENDING) and not getattr(norm, "accepts_pending", False):
         delta = delta.compute()
     return norm.add_forward(resid, delta)
 
@@ -68,3 +68,71 @@ class PreNormBlock:
         if self._feed_forward_defers:
             return self.feed_forward.forward(h, ctx, defer_output=True)
         return self.feed_forward.forward(h, ctx)
+
+
+@register_arrangement("sandwich")
+class SandwichBlock:
+    """``x += s * post_norm_1(mixer(norm_1(x))); x += s * post_norm_2(ff(norm_2(x)))``: every branch
+    is normed on its way in and on its way out, and its normed output is multiplied by the
+    layer's ``residual_scale`` s before it joins the 32-bit stream.  A layer without a
+    feed-forward has the first half only.
+
+    The branch's last product writes 32-bit sums; the post-norm of the branch, the residual sum
+    and the norm in front of the next branch are one kernel (``ops.post_norm_add``), so the block
+    hands its own last branch output on unadded, as the pre-norm arrangement does."""
+
+    accepts_pending = True
+
+    @staticmethod
+    def tensor_specs(spec: LayerSpec, prefix: str = "") -> list[TensorSpec]:
+        p = spec.prefix
+        out = (NORMS.tensor_specs(spec.mixer_norm, f"{p}.{spec.mixer_norm_prefix}")
+               + NORMS.tensor_specs(spec.mixer_post_norm, f"{p}.{spec.mixer_post_norm_prefix}")
+               + MIXERS.tensor_specs(spec.mixer, f"{p}.{spec.mixer_prefix}"))
+        if spec.feed_forward is not None:
+            out += (NORMS.tensor_specs(spec.feed_forward_norm, f"{p}.{spec.feed_forward_norm_prefix}")
+                    + NORMS.tensor_specs(spec.feed_forward_post_norm, f"{p}.{spec.feed_forward_post_norm_prefix}")
+                    + FEED_FORWARDS.tensor_specs(spec.feed_forward, f"{p}.{spec.feed_forward_prefix}"))
+        return out
+
+    def __init__(self, spec: LayerSpec, tensors, runtime: Runtime):
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and spec.feed_forward_post_norm is None):
+            raise ValueError("the sandwich arrangement needs a post-norm for every branch")
+        mine = local(tensors, spec.prefix)
+        build = lambda norm_spec, prefix: NORMS.build(norm_spec, local(mine, prefix), runtime)
+        self.scale = float(spec.residual_scale)
+        self.act = runtime.precision.act
+        self.mixer_norm = build(spec.mixer_norm, spec.mixer_norm_prefix)
+        self.mixer_post_norm = build(spec.mixer_post_norm, spec.mixer_post_norm_prefix)
+        self.mixer = MIXERS.build(spec.mixer, local(mine, spec.mixer_prefix), runtime)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = build(spec.feed_forward_norm, spec.feed_forward_norm_prefix)
+            self.feed_forward_post_norm = build(spec.feed_forward_post_norm, spec.feed_forward_post_norm_prefix)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, local(mine, spec.feed_forward_prefix), runtime)
+        self._mixer_defers = bool(getattr(self.mixer, "can_defer_output", False))
+        self._feed_forward_defers = bool(getattr(self.feed_forward, "can_defer_output", False))
+
+    def _branch(self, y, post_norm) -> "ops.PendingPostNorm":
+        """The branch output as 32-bit rows, with the post-norm that it still has to pass."""
+        if isinstance(y, ops.PendingLinear):
+            y = ops.linear(y.x, y.w, out_dtype=torch.float32)
+        elif y.dtype != torch.float32:
+            y = y.to(torch.float32)
+        return ops.PendingPostNorm(y, post_norm.weight, post_norm.eps, self.scale, self.act)
+
+    def forward(self, resid: torch.Tensor, delta, ctx, cache):
+        h = part_input(self.mixer, norm_add(self.mixer_norm, resid, delta))
+        if self._mixer_defers:
+            a = self.mixer.forward(h, ctx, cache, defer_output=True)
+        else:
+            a = self.mixer.forward(h, ctx, cache)
+        a = self._branch(a, self.mixer_post_norm)
+        if self.feed_forward is None:
+            return a
+        h = part_input(self.feed_forward, norm_add(self.feed_forward_norm, resid, a))
+        if self._feed_forward_defers:
+            f = self.feed_forward.forward(h, ctx, defer_output=True)
+        else:
+            f = self.feed_forward.forward(h, ctx)
+        return self._branch(f, self.feed_forward_post_norm)

@@ -13,25 +13,31 @@ from ..kernels import ops
 from .base import Runtime, register_feed_forward
 
 
+def _bias_name(weight_name: str):
+    """``x.weight`` -> ``x.bias``; a name without that ending has no bias beside it (None)."""
+    return weight_name[:-len("weight")] + "bias" if weight_name.endswith(".weight") else None
+
+
 @register_feed_forward("gated_mlp")
 class GatedMLP:
     accepts_normed_rows = True      # its first product takes ``ops.NormedRows`` as x
     can_defer_output = True         # ``forward(..., defer_output=True)`` may return ``ops.PendingLinear``
     @staticmethod
     def tensor_specs(spec: GatedMLPSpec, prefix: str):
-        return [
-            TensorSpec(f"{prefix}.gate_proj.weight", (spec.intermediate, spec.hidden)),
-            TensorSpec(f"{prefix}.up_proj.weight", (spec.intermediate, spec.hidden)),
-            TensorSpec(f"{prefix}.down_proj.weight", (spec.hidden, spec.intermediate)),
-            TensorSpec(f"{prefix}.gate_proj.bias", (spec.intermediate,), optional=True),
-            TensorSpec(f"{prefix}.up_proj.bias", (spec.intermediate,), optional=True),
-            TensorSpec(f"{prefix}.down_proj.bias", (spec.hidden,), optional=True),
-        ]
+        gate, up, down = spec.tensor_names
+        out = [TensorSpec(f"{prefix}.{gate}", (spec.intermediate, spec.hidden)),
+               TensorSpec(f"{prefix}.{up}", (spec.intermediate, spec.hidden)),
+               TensorSpec(f"{prefix}.{down}", (spec.hidden, spec.intermediate))]
+        for name, size in ((gate, spec.intermediate), (up, spec.intermediate), (down, spec.hidden)):
+            if name.endswith(".weight"):
+                out.append(TensorSpec(f"{prefix}.{_bias_name(name)}", (size,), optional=True))
+        return out
 
     def __init__(self, spec: GatedMLPSpec, tensors, runtime: Runtime):
         ops.gate_code(spec.activation)       # refuses a gate function no kernel has
         self.spec = spec
-        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        gate_name, up_name, down_name = spec.tensor_names
+        gate, up = tensors[gate_name], tensors[up_name]
         # bfloat16: gate and up rows interleaved in runs of eight, so that the decode GEMM's
         # epilogue finds a gate and its up in one thread and applies the activation itself
         self.interleaved = runtime.precision.act == torch.bfloat16 and spec.intermediate % 8 == 0
@@ -40,9 +46,9 @@ class GatedMLP:
             self.w_gate_up = runtime.matrix(stacked.reshape(2 * spec.intermediate, spec.hidden))
         else:
             self.w_gate_up = runtime.matrix(torch.cat([gate, up], dim=0))
-        self.w_down = runtime.matrix(tensors["down_proj.weight"])
+        self.w_down = runtime.matrix(tensors[down_name])
         self.b_gate_up = None
-        gate_bias, up_bias = tensors.get("gate_proj.bias"), tensors.get("up_proj.bias")
+        gate_bias, up_bias = tensors.get(_bias_name(gate_name)), tensors.get(_bias_name(up_name))
         if gate_bias is not None or up_bias is not None:
             zeros = torch.zeros(spec.intermediate, dtype=torch.float32)
             gate_bias = zeros if gate_bias is None else gate_bias.to(torch.float32)
@@ -52,7 +58,8 @@ class GatedMLP:
             else:
                 both = torch.cat([gate_bias, up_bias])
             self.b_gate_up = runtime.vector_f32(both)
-        self.b_down = runtime.vector_f32(tensors["down_proj.bias"]) if "down_proj.bias" in tensors else None
+        down_bias = tensors.get(_bias_name(down_name))
+        self.b_down = runtime.vector_f32(down_bias) if down_bias is not None else None
 
     def activation_elements(self) -> int:
         """Elements per token of the temporaries alive at once (gate, up and their product)."""

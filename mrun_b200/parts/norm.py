@@ -16,7 +16,7 @@ from .base import Runtime, register_norm
 class RMSNorm:
     @staticmethod
     def tensor_specs(spec: RMSNormSpec, prefix: str):
-        return [TensorSpec(f"{prefix}.weight", (spec.size,), "norm")]
+        return [TensorSpec(prefix if spec.bare else f"{prefix}.weight", (spec.size,), "norm")]
 
     # ``delta`` may be a product that has not run yet (``ops.PendingLinear``): with a handful
     # of rows it runs with the residual sum and this norm folded into its epilogue, and what
@@ -26,10 +26,16 @@ class RMSNorm:
 
     def __init__(self, spec: RMSNormSpec, tensors, runtime: Runtime):
         self.size, self.eps = spec.size, float(spec.eps)
-        self.weight = runtime.vector_f32(tensors["weight"])
+        self.weight = runtime.vector_f32(tensors["" if spec.bare else "weight"])
         self.act = runtime.precision.act
 
     def add_forward(self, resid: torch.Tensor, delta):
+        if isinstance(delta, ops.PendingPostNorm):
+            # a branch output that is normed and scaled before it joins the stream: one kernel
+            # norms it, adds it and norms the new rows with this norm's weight
+            out = torch.empty(resid.shape, dtype=self.act, device=resid.device)
+            return ops.post_norm_add(resid, delta.branch, delta.weight, delta.scale, delta.eps, self.weight,
+                                     self.eps, out)
         if isinstance(delta, ops.PendingLinear):
             if ops.norm_fusable(delta, resid, self.weight):
                 return ops.linear_into_norm(delta, resid, self.weight, self.eps)
@@ -42,6 +48,10 @@ class RMSNorm:
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
 
     def rows_forward(self, resid: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        if isinstance(delta, ops.PendingPostNorm):
+            out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)
+            return ops.post_norm_add(resid, delta.branch, delta.weight, delta.scale, delta.eps, self.weight,
+                                     self.eps, out, rows=rows)
         if isinstance(delta, ops.PendingLinear):
             delta = delta.compute()
         out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)

@@ -1,0 +1,60 @@
+"""A routed feed-forward: a mixture of small experts ``down(act(up(x)))`` and an optional shared
+expert of the same form.
+
+The router's logits and scores are 32-bit (``ops.route_top_k``: the score of every expert, the
+``top`` largest chosen, their scores kept as the experts' weights and zero for the rest).  The
+experts' up-projections are stacked into one matrix, the shared expert's rows after them, and so
+are the columns of the down-projections: a step is the router product, the routing kernel, one
+product up, one kernel that applies relu^2 and the token's weight of the column's expert (zero
+for an expert the token did not choose, one for the shared expert), and one product down, which
+sums the weighted experts and the shared expert in its 32-bit accumulator.  Every token's result
+depends on its own row only.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import RoutedMLPSpec, TensorSpec
+from ..kernels import ops
+from .base import Runtime, register_feed_forward
+
+ACTIVATIONS = ("relu2",)
+
+
+@register_feed_forward("routed_mlp")
+class RoutedMLP:
+    can_defer_output = True         # ``forward(..., defer_output=True)`` may return ``ops.PendingLinear``
+
+    @staticmethod
+    def tensor_specs(spec: RoutedMLPSpec, prefix: str):
+        out = [TensorSpec(f"{prefix}.router", (spec.experts, spec.hidden))]
+        for e in range(spec.experts):
+            out += [TensorSpec(f"{prefix}.e{e}.up", (spec.expert_ff, spec.hidden)),
+                    TensorSpec(f"{prefix}.e{e}.down", (spec.hidden, spec.expert_ff))]
+        if spec.shared_ff:
+            out += [TensorSpec(f"{prefix}.shared.up", (spec.shared_ff, spec.hidden)),
+                    TensorSpec(f"{prefix}.shared.down", (spec.hidden, spec.shared_ff))]
+        return out
+
+    def __init__(self, spec: RoutedMLPSpec, tensors, runtime: Runtime):
+        if spec.activation not in ACTIVATIONS:
+            raise ValueError(f"no kernel has the expert activation {spec.activation!r} (known: {', '.join(ACTIVATIONS)})")
+        if spec.score not in ops.ROUTER_SCORES:
+            raise ValueError(f"no kernel has the router score {spec.score!r}")
+        self.spec = spec
+        names = [f"e{e}" for e in range(spec.experts)] + (["shared"] if spec.shared_ff else [])
+        self.w_router = runtime.matrix(tensors["router"])
+        self.w_up = runtime.matrix(torch.cat([tensors[f"{n}.up"] for n in names], dim=0))
+        self.w_down = runtime.matrix(torch.cat([tensors[f"{n}.down"] for n in names], dim=1))
+
+    def activation_elements(self) -> int:
+        return 2 * (self.spec.experts * self.spec.expert_ff + self.spec.shared_ff) + self.spec.experts
+
+    def forward(self, x, ctx, defer_output: bool = False):
+        s = self.spec
+        logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
+        weights = ops.route_top_k(logits, s.top, s.score, s.renormalize)
+        act = ops.relu2_scaled(ops.linear(x, self.w_up), weights, s.experts, s.expert_ff)
+        if defer_output:
+            return ops.linear_or_pending(act, self.w_down)
+        return ops.linear(act, self.w_down)

@@ -37,6 +37,8 @@ def supported() -> list[str]:
 def resolve(cfg: Mapping[str, Any], where: Optional[str] = None) -> type:
     """The configuration class that ``cfg`` names."""
     architectures = cfg.get("architectures")
+    if isinstance(cfg.get("architecture"), str):          # some designs name themselves by one string
+        architectures = [cfg["architecture"]] + (architectures if isinstance(architectures, list) else [])
     if isinstance(architectures, list):
         for name in architectures:
             if name in _BY_ARCHITECTURE:
@@ -62,7 +64,9 @@ def load_config(model_dir: str):
 
 def _register_builtin() -> None:
     from .config.qwen3 import Qwen3Config
+    from .config.zasesun import ZasesunConfig
     register_architecture(Qwen3Config)
+    register_architecture(ZasesunConfig)
 
 
 _register_builtin()
