@@ -91,10 +91,17 @@ def expert(h, w, prefix):
     return torch.relu(h @ g("up").T) ** 2 @ g("down").T
 
 
-def routed_feed_forward(h, w, prefix, mlp):
+def routed_feed_forward(h, w, prefix, mlp, margins=None):
+    """``margins`` (a list) gets, per token, how far the router's logit of the last expert chosen
+    lies above that of the first one left out (infinite when every expert is chosen)."""
     experts, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    scores = torch.softmax(h @ w[f"{prefix}.router"].to(h.dtype).T, dim=-1)         # [tokens, experts]
+    logits = h @ w[f"{prefix}.router"].to(h.dtype).T
+    scores = torch.softmax(logits, dim=-1)                                          # [tokens, experts]
     chosen = torch.topk(scores, top, dim=-1).indices
+    if margins is not None:
+        ranked = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < experts
+                       else torch.full((h.shape[0],), float("inf"), dtype=h.dtype))
     out = torch.zeros_like(h)
     for e in range(experts):
         uses = (chosen == e).any(-1)
@@ -105,11 +112,11 @@ def routed_feed_forward(h, w, prefix, mlp):
     return out
 
 
-def feed_forward(h, w, prefix, mlp):
+def feed_forward(h, w, prefix, mlp, margins=None):
     if mlp["kind"] == "dense":
         return dense_feed_forward(h, w, prefix)
     if mlp["kind"] == "moe":
-        return routed_feed_forward(h, w, prefix, mlp)
+        return routed_feed_forward(h, w, prefix, mlp, margins)
     raise ValueError(mlp["kind"])
 
 
@@ -117,8 +124,10 @@ def soft_cap(logits, cap):
     return cap * torch.tanh(logits / cap)
 
 
-def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
-    """Logits [tokens, vocab] of one sequence of token ids (and the stream after every layer)."""
+def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False, margins=None):
+    """Logits [tokens, vocab] of one sequence of token ids (and the stream after every layer).
+    ``margins``: a list that gets every routed layer's router margins (see
+    :func:`routed_feed_forward`)."""
     eps, m = float(cfg["norm"]["eps"]), float(cfg["residual_mult"])
     ids = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(len(ids))
@@ -132,7 +141,7 @@ def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False):
         a = latent_attention(norm(x, "norm1"), w, f"{p}.mix", layer["mixer"], eps, positions)
         x = x + m * norm(a, "norm1b")
         if layer.get("mlp"):
-            f = feed_forward(norm(x, "norm2"), w, f"{p}.mlp", layer["mlp"])
+            f = feed_forward(norm(x, "norm2"), w, f"{p}.mlp", layer["mlp"], margins)
             x = x + m * norm(f, "norm2b")
         after.append(x)
     logits = rms_norm(x, w["final.norm"].to(dtype), eps) @ w["embed"].to(dtype).T
