@@ -3,7 +3,7 @@
 random weights and seeded synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
-                    [--shape 8b|4b|32b] [--serve]
+                    [--shape 8b|4b|32b] [--serve] [--design zasesun]
 
 A *step* is one decode step of a batch of 8 requests that each hold 1,024 tokens of context.
 ``value`` is decoded tokens per second over exactly K steps, timed on the device with CUDA events
@@ -13,6 +13,9 @@ The line also carries a 2,048-token prefill, the decode step's HBM roofline, and
 1 and 64.  Weights (15 GB) are far larger than L2, so every step reads them from HBM.
 ``--shape`` runs the same at the 4B or 32B layer sizes (the 32B at 2,048 tokens of context and
 batch 1, 8 and 32), and ``--serve`` times a mixed workload of 16 requests through the scheduler.
+``--design zasesun`` measures the Zasesun decoder (latent attention, sandwich norms, dense and
+routed feed-forwards) beside the Qwen3 decoder at equal widths, depths and head counts: prefill of
+2,048 tokens and decode at batch 8, each with its own FLOP and byte counts against the peaks.
 """
 from __future__ import annotations
 
@@ -227,6 +230,129 @@ def serve(args, config, model_name: str, full_layers: int, page_size: int, peaks
     return 0
 
 
+# Layer sizes for --design: (name, Zasesun sizes, the Qwen3 sizes of equal width, depth and heads).
+# The cache row of the latent attention (kv_rank + rot_dim) is 128, 256 and 576 features: the
+# first two are head sizes the tensor-core attention kernels are built for, the third is not.
+def _zasesun_sizes(width, heads, dim, rot_dim, vdim, q_rank, kv_rank, ff, experts, top, expert_ff, shared_ff,
+                   layers, vocab):
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+             "scale": (dim + rot_dim) ** -0.5,
+             "rot": {"base": 10000.0, "dims": rot_dim,
+                     "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff},
+           "shared": {"ff": shared_ff}}
+    return {"architecture": "Zasesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_softcap": 30.0,
+            "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe}
+                       for i in range(layers)]}
+
+
+DESIGN_SIZES = {
+    "row128": (_zasesun_sizes(2048, 16, 64, 32, 64, 768, 96, 8192, 8, 2, 2048, 2048, 8, 32768),
+               dict(QWEN3_8B, num_hidden_layers=8, hidden_size=2048, num_attention_heads=16, num_key_value_heads=2,
+                    head_dim=128, intermediate_size=8192, vocab_size=32768, tie_word_embeddings=True)),
+    "row256": (_zasesun_sizes(4096, 16, 128, 64, 128, 1536, 192, 12288, 8, 2, 3072, 3072, 8, 32768),
+               dict(QWEN3_8B, num_hidden_layers=8, hidden_size=4096, num_attention_heads=16, num_key_value_heads=2,
+                    head_dim=128, intermediate_size=12288, vocab_size=32768, tie_word_embeddings=True)),
+    "row576": (_zasesun_sizes(2048, 16, 128, 64, 128, 1536, 512, 8192, 8, 2, 2048, 2048, 4, 32768),
+               dict(QWEN3_8B, num_hidden_layers=4, hidden_size=2048, num_attention_heads=16, num_key_value_heads=2,
+                    head_dim=128, intermediate_size=8192, vocab_size=32768, tie_word_embeddings=True)),
+}
+
+
+def zasesun_counts(cfg: dict, tokens: int):
+    """(FLOPs of a prompt of ``tokens`` tokens as the design states them, bytes of one token's
+    cache rows over all layers) of a Zasesun configuration: products count two FLOPs a weight and
+    token, a routed layer its chosen and its shared experts only, attention the scores over the
+    cache row and the weighted sum over the latent for every visible key."""
+    h, flops, row_bytes = cfg["width"], 0.0, 0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        params = ((m["q_rank"] + m["kv_rank"] + m["rot_dim"]) * h + m["heads"] * (m["dim"] + m["rot_dim"]) * m["q_rank"]
+                  + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"] + h * m["heads"] * m["vdim"])
+        mlp = layer["mlp"]
+        if mlp and mlp["kind"] == "dense":
+            params += 3 * h * mlp["ff"]
+        elif mlp:
+            params += 2 * h * (mlp["router"]["top"] * mlp["expert"]["ff"] + mlp["shared"]["ff"]) + h * mlp["router"]["experts"]
+        flops += 2.0 * tokens * params + 2.0 * (tokens * tokens / 2.0) * m["heads"] * (2 * m["kv_rank"] + m["rot_dim"])
+        row_bytes += 2 * (-(-(m["kv_rank"] + m["rot_dim"]) // 16) * 16)
+    return flops + 2.0 * cfg["vocab"] * h, row_bytes
+
+
+def compare_designs(args, peaks: dict) -> int:
+    """Prefill of 2,048 tokens and decode at batch 8 with 1,024-token contexts, Zasesun beside
+    Qwen3 at equal sizes, each through the same ``Executor.step`` and captured decode step."""
+    import torch
+    from mrun_b200 import Engine
+    from mrun_b200.config import Qwen3Config, ZasesunConfig
+    from mrun_b200.engine import StepEntry
+    context, batch = 1024, 8
+    out = {}
+    sampler = ClockSampler()
+    sampler.start()
+    for name in (args.sizes.split(",") if args.sizes else sorted(DESIGN_SIZES)):
+        z_sizes, q_sizes = DESIGN_SIZES[name]
+        row = {}
+        for design in ("zasesun", "qwen3"):
+            if design == "zasesun":
+                config = ZasesunConfig.from_dict(z_sizes)
+                vocab, h = z_sizes["vocab"], z_sizes["width"]
+                flops, kv_bytes = zasesun_counts(z_sizes, PREFILL_TOKENS)
+            else:
+                config = Qwen3Config(**dict(q_sizes, max_position_embeddings=8192))
+                vocab, h, d = config.vocab_size, config.hidden_size, config.head_dim
+                params = config.num_hidden_layers * ((2 * config.num_attention_heads + 2 * config.num_key_value_heads) * d * h
+                                                     + 3 * h * config.intermediate_size)
+                flops = 2.0 * PREFILL_TOKENS * params + 2.0 * vocab * h \
+                    + config.num_hidden_layers * 2.0 * PREFILL_TOKENS ** 2 * config.num_attention_heads * d
+                kv_bytes = config.kv_bytes_per_token(2)
+            slack = args.steps * 2 + args.warmup + 64
+            capacity = batch * (context + slack) + PREFILL_TOKENS + 256
+            engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_size=args.page_size,
+                                        num_pages=-(-capacity // args.page_size), max_requests=16,
+                                        max_batch_tokens=PREFILL_TOKENS)
+            executor = engine.executor
+            prompt, times = seeded_tokens(vocab, PREFILL_TOKENS, 3), []
+            for i in range(5):
+                request = executor.admit(("prefill", i))
+                torch.cuda.synchronize()
+                begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                begin.record()
+                executor.step([StepEntry(request, prompt, [PREFILL_TOKENS - 1])])
+                end.record()
+                torch.cuda.synchronize()
+                executor.release(request)
+                if i >= 2:
+                    times.append(begin.elapsed_time(end))
+            prefill_ms = statistics.median(times)
+            requests = fill_requests(executor, batch, context, vocab, "decode")
+            decode_times, launches = time_decode(executor, requests, vocab, args.steps, args.warmup, repeats=2)
+            ms = statistics.median(decode_times) / args.steps
+            weight_bytes = executor.model.weight_bytes()
+            step_bytes = weight_bytes + batch * (context + args.warmup + args.steps) * kv_bytes
+            row[design] = {
+                "layers": len(executor.model.order), "weights_gb": round(weight_bytes / 1e9, 2),
+                "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                "prefill_frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                "decode_b8_tok_s": round(batch / (ms * 1e-3), 1), "decode_ms_per_step": round(ms, 4),
+                "decode_frac": round(step_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                "decode_launches": launches // max(1, args.steps), "cache_bytes_per_token": kv_bytes}
+            for r in requests:
+                executor.release(r)
+            del engine, executor, requests
+            torch.cuda.empty_cache()
+        out[name] = row
+    print(json.dumps({"metric": "prefill and decode tok/s, Zasesun beside Qwen3 at equal sizes (bf16)", "unit": "tok/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
+                      "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
+                      "config": {"prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "context": context,
+                                 "page_size": args.page_size, "of": peaks["source"]},
+                      "sizes": out, "clocks": sampler.stop(), "peaks": peaks}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -256,6 +382,10 @@ def main() -> int:
     parser.add_argument("--profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                         help="bracket the timed decode steps (or the last timed prefill) with "
                              "cudaProfilerStart/Stop, for a profiler started with --profile-from-start off")
+    parser.add_argument("--design", choices=["zasesun"], default=None,
+                        help="instead of the default workload: the named design beside Qwen3 at equal sizes "
+                             "(prefill of 2,048 tokens, decode at batch 8)")
+    parser.add_argument("--sizes", default=None, help="with --design: which of its size sets to run, comma separated")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -275,6 +405,8 @@ def main() -> int:
     from mrun_b200.kernels import lib as kernel_lib
 
     peaks = load_peaks()
+    if args.design:
+        return compare_designs(args, peaks)
     model_name, shape_sizes, shape_context = SHAPES[args.shape]
     sizes = dict(shape_sizes)
     if args.context is None:

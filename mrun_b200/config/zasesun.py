@@ -159,6 +159,17 @@ class ZasesunConfig:
         return out
 
     # ------------------------------------------------------------------ derived
+    def num_parameters(self) -> int:
+        """Elements of every tensor the checkpoint holds."""
+        from ..weights.loader import expected_tensors
+        total = 0
+        for t in expected_tensors(self.to_spec()):
+            count = 1
+            for extent in t.shape:
+                count *= extent
+            total += count
+        return total
+
     def to_spec(self) -> ModelSpec:
         norm = RMSNormSpec(self.width, self.eps, bare=True)
         layers = tuple(

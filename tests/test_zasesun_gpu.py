@@ -392,3 +392,30 @@ def test_greedy_generation_matches_plain(ztiny, dtype):
             tokens.append(token)
     engine.executor.cache.check_invariants()
     assert not engine.executor.cache.live
+
+
+def test_command_line_random_then_run(tmp_path):
+    """``mrun random`` writes a Zasesun folder from its config.json, ``mrun run`` generates from it."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir))
+    mrun = os.path.join(root, "bin", "mrun")
+    run = lambda *args: subprocess.run([sys.executable, mrun, *args], capture_output=True, text=True, timeout=600)
+    (tmp_path / "cfg.json").write_text(json.dumps(ZTINY["P"]["config"]))
+    folder = str(tmp_path / "model")
+    made = run("random", folder, "--config", str(tmp_path / "cfg.json"), "--seed", "21", "--std", "0.1")
+    assert made.returncode == 0, made.stderr
+    cfg, weights = load_folder(folder)
+    prompt = tokens_of(cfg["vocab"], 19, seed=8)
+    result = run("run", folder, "--prompt", ",".join(map(str, prompt)), "--max-tokens", "6", "--dtype", "float32",
+                 "--ignore-eos", "--context", "1K")
+    assert result.returncode == 0, result.stderr
+    tokens = list(prompt)
+    for token in (int(t) for t in result.stdout.strip().split(",")):
+        logits = plain.forward(cfg, weights, tokens)[-1]
+        best = int(torch.argmax(logits))
+        assert token == best or float(logits[best] - logits[token]) < 1e-3
+        tokens.append(token)
+    assert len(tokens) == 19 + 6 and "Zasesun" in result.stderr
