@@ -38,21 +38,22 @@ latent_prepare_kernel(const TA* __restrict__ down, long ld, const float* __restr
     __shared__ float scratch[33];
     const int t = blockIdx.x, tid = threadIdx.x;
     const TA* row = down + (size_t)t * ld;
+    const TA* kv = row + q_rank;
+    const int slot = slots ? slots[t] : -1;      // negative: a padding row, or a run that only reads another's cache
+    // both totals of squares from one sweep over the row, so that the block waits for memory once
+    float ss_q = 0.f, ss_kv = 0.f;
+    for (int i = tid; i < q_rank; i += blockDim.x) { const float v = to_float(row[i]); ss_q += v * v; }
+    if (slot >= 0)
+        for (int i = tid; i < kv_rank; i += blockDim.x) { const float v = to_float(kv[i]); ss_kv += v * v; }
     if (q_rank > 0) {
-        float ss = 0.f;
-        for (int i = tid; i < q_rank; i += blockDim.x) { const float v = to_float(row[i]); ss += v * v; }
-        ss = block_sum(ss, scratch);
-        const float inv = rsqrtf(ss / (float)q_rank + eps);
+        ss_q = block_sum(ss_q, scratch);
+        const float inv = rsqrtf(ss_q / (float)q_rank + eps);
         for (int i = tid; i < q_rank; i += blockDim.x)
             cq[(size_t)t * q_rank + i] = from_float<TA>(to_float(row[i]) * inv * q_weight[i]);
     }
-    const int slot = slots ? slots[t] : -1;
-    if (slot < 0) return;        // a padding row, or a run that only reads another's cache
-    const TA* kv = row + q_rank;
-    float ss = 0.f;
-    for (int i = tid; i < kv_rank; i += blockDim.x) { const float v = to_float(kv[i]); ss += v * v; }
-    ss = block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / (float)kv_rank + eps);
+    if (slot < 0) return;
+    ss_kv = block_sum(ss_kv, scratch);
+    const float inv = rsqrtf(ss_kv / (float)kv_rank + eps);
     TA* dst = cache + (size_t)slot * width;
     for (int i = tid; i < kv_rank; i += blockDim.x)
         dst[i] = from_float<TA>(to_float(kv[i]) * inv * kv_weight[i]);
@@ -136,6 +137,65 @@ post_norm_add_kernel(float* __restrict__ stream, const float* __restrict__ branc
     TA* dst = out + (size_t)r * hidden;
     for (int h = threadIdx.x; h < hidden; h += blockDim.x)
         dst[h] = from_float<TA>(row_buf[h] * inv_v * w_next[h]);
+}
+
+// The same for widths that are a multiple of 8 and at most 8192: a thread keeps up to four
+// 8-value chunks of the stream and of the branch in registers, so a row is read once, with all its
+// loads in flight together.  One block of 256 threads a row: the order of additions depends on
+// the width only.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+post_norm_add_vec_kernel(float* __restrict__ stream, const float* __restrict__ branch,
+                         const float* __restrict__ w_post, float scale, float eps_post,
+                         const float* __restrict__ w_next, float eps_next, TA* __restrict__ out,
+                         const int* __restrict__ rows, int hidden) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    const int chunks = hidden >> 3;
+    float v[4][8], b[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < chunks) {
+            Vec8<float>::load(branch + src + c * 8, b[i]);
+            Vec8<float>::load(stream + src + c * 8, v[i]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += b[i][e] * b[i][e];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv_b = rsqrtf(ss / (float)hidden + eps_post) * scale;
+    float sv = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < chunks) {
+            float w[8];
+            Vec8<float>::load(w_post + c * 8, w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[i][e] += b[i][e] * inv_b * w[e];
+                sv += v[i][e] * v[i][e];
+            }
+            if (!rows) Vec8<float>::store(stream + src + c * 8, v[i]);
+        }
+    }
+    if (!w_next) return;
+    sv = block_sum(sv, scratch);
+    const float inv_v = rsqrtf(sv / (float)hidden + eps_next);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < chunks) {
+            float w[8], y[8];
+            Vec8<float>::load(w_next + c * 8, w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = v[i][e] * inv_v * w[e];
+            Vec8<TA>::store(out + (size_t)r * hidden + c * 8, y);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -234,6 +294,27 @@ __global__ void relu2_scaled_kernel(const TA* __restrict__ u, TA* __restrict__ a
     act[i] = from_float<TA>(v * v * w);
 }
 
+// Eight columns a thread, for column counts and expert sizes that are multiples of 8 (a chunk then
+// lies inside one expert): grid.x walks the tokens, grid.y the chunks of a row.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+relu2_scaled_vec_kernel(const TA* __restrict__ u, TA* __restrict__ act, const float* __restrict__ weights,
+                        int columns, int experts, int ff) {
+    const long t = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= columns) return;
+    const int e = c / ff;
+    const float w = (weights && e < experts) ? weights[t * experts + e] : 1.f;
+    float v[8];
+    Vec8<TA>::load(u + t * columns + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float x = fmaxf(v[i], 0.f);
+        v[i] = x * x * w;
+    }
+    Vec8<TA>::store(act + t * columns + c, v);
+}
+
 __global__ void soft_cap_kernel(float* __restrict__ x, long total, float cap) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) x[i] = cap * tanhf(x[i] / cap);
@@ -297,6 +378,18 @@ MRUN_API int mrun_post_norm_add(float* stream_rows, const float* branch, const f
     MRUN_REQUIRE(hidden <= 12 * 1024, "post_norm_add: hidden=%d exceeds the supported 12288", hidden);
     MRUN_REQUIRE(w_next == nullptr || out != nullptr, "post_norm_add: a next norm needs an output");
     if (n_rows == 0) return 0;
+    const bool aligned = (((uintptr_t)stream_rows | (uintptr_t)branch | (uintptr_t)w_post | (uintptr_t)w_next |
+                           (uintptr_t)out) & 15) == 0;
+    if (hidden % 8 == 0 && hidden <= 8192 && aligned && (act_dtype == MRUN_F32 || act_dtype == MRUN_BF16)) {
+        if (act_dtype == MRUN_F32)
+            post_norm_add_vec_kernel<float><<<n_rows, 256, 0, stream>>>(stream_rows, branch, w_post, scale, eps_post,
+                                                                        w_next, eps_next, (float*)out, rows, hidden);
+        else
+            post_norm_add_vec_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>(
+                stream_rows, branch, w_post, scale, eps_post, w_next, eps_next, (__nv_bfloat16*)out, rows, hidden);
+        MRUN_CHECK_LAUNCH("post_norm_add");
+        return 0;
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (act_dtype == MRUN_F32)
         post_norm_add_kernel<float><<<n_rows, 256, smem, stream>>>(stream_rows, branch, w_post, scale, eps_post,
@@ -330,6 +423,20 @@ MRUN_API int mrun_relu2_scaled(const void* u, void* act, int act_dtype, const fl
                  "relu2_scaled: bad sizes columns=%d experts=%d ff=%d", columns, experts, ff);
     const long total = (long)tokens * columns;
     if (total == 0) return 0;
+    const bool aligned = (((uintptr_t)u | (uintptr_t)act) & 15) == 0;
+    const int chunk_blocks = (columns / 8 + 255) / 256;
+    if (columns % 8 == 0 && ff % 8 == 0 && aligned && chunk_blocks <= 65535 &&
+        (act_dtype == MRUN_F32 || act_dtype == MRUN_BF16)) {
+        const dim3 grid(tokens, chunk_blocks);
+        if (act_dtype == MRUN_F32)
+            relu2_scaled_vec_kernel<float><<<grid, 256, 0, stream>>>((const float*)u, (float*)act, weights, columns,
+                                                                     experts, ff);
+        else
+            relu2_scaled_vec_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+                (const __nv_bfloat16*)u, (__nv_bfloat16*)act, weights, columns, experts, ff);
+        MRUN_CHECK_LAUNCH("relu2_scaled");
+        return 0;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (act_dtype == MRUN_F32)
         relu2_scaled_kernel<float><<<blocks, 256, 0, stream>>>((const float*)u, (float*)act, weights, total, columns,

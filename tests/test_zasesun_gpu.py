@@ -128,6 +128,10 @@ def test_relu2_soft_cap_and_per_head_products(dtype):
     factor = torch.cat([weights.cpu().double().repeat_interleave(7, dim=1), torch.ones(11, 5, dtype=F64)], dim=1)
     close(got, torch.relu(u.cpu().double()) ** 2 * factor, dtype, "relu2 with weights")
     close(ops.relu2_scaled(u, None, 0, 1), torch.relu(u.cpu().double()) ** 2, dtype, "relu2 alone")
+    wide = torch.randn(300, 5 * 16 + 24, device=DEV).to(act)          # eight columns a thread
+    wide_weights = torch.rand(300, 5, device=DEV)
+    factor = torch.cat([wide_weights.cpu().double().repeat_interleave(16, dim=1), torch.ones(300, 24, dtype=F64)], dim=1)
+    close(ops.relu2_scaled(wide, wide_weights, 5, 16), torch.relu(wide.cpu().double()) ** 2 * factor, dtype, "relu2, wide rows")
     x = torch.randn(6, 50, device=DEV) * 20
     close(ops.soft_cap(x.clone(), 7.0), plain.soft_cap(x.cpu().double(), 7.0), "float32", "soft cap")
     # heads side by side in wider rows, in and out
