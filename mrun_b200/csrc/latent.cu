@@ -23,43 +23,58 @@ __device__ __forceinline__ void pair_features(int i, int dims, int interleaved, 
 }
 
 // ------------------------------------------------------------------------------------------
-// One block a token.  down[t] = [query latent (q_rank) | key/value latent (kv_rank) | shared key
+// One warp a token.  down[t] = [query latent (q_rank) | key/value latent (kv_rank) | shared key
 // part (rot_dim)], the stacked down-projections' output.  The two latents are RMS-normed with
 // their weights (eps inside the root); the shared key part is not normed, its first `rot_dims`
 // features rotate by the token's table row.  The cache row of width `width` >= kv_rank + rot_dim
 // is filled to its end with zeros, so that an attention kernel may take it as a key of that size.
+// A warp sums in a fixed order (lane-strided, then a butterfly), so a token's result does not
+// depend on the batch; it asks for the norm weights and its table row while the row's values
+// are on their way, and meets no block-wide barrier.
 // ------------------------------------------------------------------------------------------
+constexpr int PREPARE_WARPS = 4;
+
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
 template <typename TA>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(PREPARE_WARPS * 32)
 latent_prepare_kernel(const TA* __restrict__ down, long ld, const float* __restrict__ q_weight,
                       const float* __restrict__ kv_weight, float eps, const float2* __restrict__ rot,
                       int rot_dims, int interleaved, const int* __restrict__ slots, TA* __restrict__ cq,
-                      TA* __restrict__ cache, int q_rank, int kv_rank, int rot_dim, int width) {
-    __shared__ float scratch[33];
-    const int t = blockIdx.x, tid = threadIdx.x;
+                      TA* __restrict__ cache, int tokens, int q_rank, int kv_rank, int rot_dim, int width) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * PREPARE_WARPS + (threadIdx.x >> 5);
+    if (t >= tokens) return;
     const TA* row = down + (size_t)t * ld;
     const TA* kv = row + q_rank;
     const int slot = slots ? slots[t] : -1;      // negative: a padding row, or a run that only reads another's cache
-    // both totals of squares from one sweep over the row, so that the block waits for memory once
+    const int pairs = rot_dims / 2;
     float ss_q = 0.f, ss_kv = 0.f;
-    for (int i = tid; i < q_rank; i += blockDim.x) { const float v = to_float(row[i]); ss_q += v * v; }
-    if (slot >= 0)
-        for (int i = tid; i < kv_rank; i += blockDim.x) { const float v = to_float(kv[i]); ss_kv += v * v; }
+    for (int i = lane; i < q_rank; i += 32) {
+        const float v = to_float(row[i]);
+        ss_q += v * v;
+        prefetch_l1(q_weight + i);
+    }
+    if (slot >= 0) {
+        for (int i = lane; i < kv_rank; i += 32) {
+            const float v = to_float(kv[i]);
+            ss_kv += v * v;
+            prefetch_l1(kv_weight + i);
+        }
+        for (int i = lane; i < pairs; i += 32) prefetch_l1(rot + (size_t)t * pairs + i);
+    }
     if (q_rank > 0) {
-        ss_q = block_sum(ss_q, scratch);
-        const float inv = rsqrtf(ss_q / (float)q_rank + eps);
-        for (int i = tid; i < q_rank; i += blockDim.x)
+        const float inv = rsqrtf(warp_sum(ss_q) / (float)q_rank + eps);
+        for (int i = lane; i < q_rank; i += 32)
             cq[(size_t)t * q_rank + i] = from_float<TA>(to_float(row[i]) * inv * q_weight[i]);
     }
     if (slot < 0) return;
-    ss_kv = block_sum(ss_kv, scratch);
-    const float inv = rsqrtf(ss_kv / (float)kv_rank + eps);
+    const float inv = rsqrtf(warp_sum(ss_kv) / (float)kv_rank + eps);
     TA* dst = cache + (size_t)slot * width;
-    for (int i = tid; i < kv_rank; i += blockDim.x)
+    for (int i = lane; i < kv_rank; i += 32)
         dst[i] = from_float<TA>(to_float(kv[i]) * inv * kv_weight[i]);
     const TA* kr = kv + kv_rank;
-    const int pairs = rot_dims / 2;
-    for (int i = tid; i < pairs; i += blockDim.x) {
+    for (int i = lane; i < pairs; i += 32) {
         int a, b;
         pair_features(i, rot_dims, interleaved, a, b);
         const float2 cs = rot[(size_t)t * pairs + i];
@@ -67,8 +82,8 @@ latent_prepare_kernel(const TA* __restrict__ down, long ld, const float* __restr
         dst[kv_rank + a] = from_float<TA>(u * cs.x - v * cs.y);
         dst[kv_rank + b] = from_float<TA>(v * cs.x + u * cs.y);
     }
-    for (int i = rot_dims + tid; i < rot_dim; i += blockDim.x) dst[kv_rank + i] = kr[i];
-    for (int i = kv_rank + rot_dim + tid; i < width; i += blockDim.x) dst[i] = from_float<TA>(0.f);
+    for (int i = rot_dims + lane; i < rot_dim; i += 32) dst[kv_rank + i] = kr[i];
+    for (int i = kv_rank + rot_dim + lane; i < width; i += 32) dst[i] = from_float<TA>(0.f);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -206,6 +221,8 @@ post_norm_add_vec_kernel(float* __restrict__ stream, const float* __restrict__ b
 // ------------------------------------------------------------------------------------------
 constexpr int ROUTE_MAX_PER_LANE = 16;      // experts <= 512
 
+// PER_LANE: experts a lane holds (experts <= 32 * PER_LANE)
+template <int PER_LANE>
 __global__ void __launch_bounds__(128)
 route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights, int* __restrict__ chosen,
                    int tokens, int experts, int top, int kind, int renormalize) {
@@ -213,10 +230,10 @@ route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= tokens) return;
     const float* z = logits + (size_t)t * experts;
-    float s[ROUTE_MAX_PER_LANE];
+    float s[PER_LANE];
     float m = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+    for (int i = 0; i < PER_LANE; ++i) {
         const int e = lane + 32 * i;
         s[i] = e < experts ? z[e] : -INFINITY;
         m = fmaxf(m, s[i]);
@@ -225,31 +242,31 @@ route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights
         m = warp_max(m);
         float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        for (int i = 0; i < PER_LANE; ++i) {
             const int e = lane + 32 * i;
             s[i] = e < experts ? expf(s[i] - m) : 0.f;
             sum += s[i];
         }
         sum = warp_sum(sum);
 #pragma unroll
-        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) s[i] = s[i] / sum;
+        for (int i = 0; i < PER_LANE; ++i) s[i] = s[i] / sum;
     } else {
 #pragma unroll
-        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        for (int i = 0; i < PER_LANE; ++i) {
             const int e = lane + 32 * i;
             s[i] = e < experts ? 1.f / (1.f + expf(-s[i])) : 0.f;
         }
     }
-    float w[ROUTE_MAX_PER_LANE];
+    float w[PER_LANE];
     unsigned taken = 0;
     float total = 0.f;
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) w[i] = 0.f;
+    for (int i = 0; i < PER_LANE; ++i) w[i] = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -1.f;
         int best_e = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        for (int i = 0; i < PER_LANE; ++i) {
             const int e = lane + 32 * i;
             if (e < experts && !(taken >> i & 1u) && s[i] > best) { best = s[i]; best_e = e; }
         }
@@ -262,7 +279,7 @@ route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights
         if ((best_e & 31) == lane) {
             const int i = best_e >> 5;
 #pragma unroll
-            for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j)
+            for (int j = 0; j < PER_LANE; ++j)
                 if (j == i) { w[j] = best; taken |= 1u << j; }
         }
         total += best;
@@ -270,7 +287,7 @@ route_top_k_kernel(const float* __restrict__ logits, float* __restrict__ weights
     }
     const float norm = renormalize ? 1.f / total : 1.f;
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+    for (int i = 0; i < PER_LANE; ++i) {
         const int e = lane + 32 * i;
         if (e < experts) weights[(size_t)t * experts + e] = w[i] * norm;
     }
@@ -333,14 +350,15 @@ MRUN_API int mrun_latent_prepare(const void* down, int act_dtype, long ld, const
     MRUN_REQUIRE(ld >= q_rank + kv_rank + rot_dim, "latent_prepare: row stride %ld below the row's width", ld);
     MRUN_REQUIRE(rot_dims == 0 || rot != nullptr, "latent_prepare: no rotation table");
     if (tokens == 0) return 0;
+    const int blocks = (tokens + PREPARE_WARPS - 1) / PREPARE_WARPS;
     if (act_dtype == MRUN_F32)
-        latent_prepare_kernel<float><<<tokens, 256, 0, stream>>>(
+        latent_prepare_kernel<float><<<blocks, PREPARE_WARPS * 32, 0, stream>>>(
             (const float*)down, ld, q_weight, kv_weight, eps, (const float2*)rot, rot_dims, interleaved, slots,
-            (float*)cq, (float*)cache, q_rank, kv_rank, rot_dim, width);
+            (float*)cq, (float*)cache, tokens, q_rank, kv_rank, rot_dim, width);
     else if (act_dtype == MRUN_BF16)
-        latent_prepare_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+        latent_prepare_kernel<__nv_bfloat16><<<blocks, PREPARE_WARPS * 32, 0, stream>>>(
             (const __nv_bfloat16*)down, ld, q_weight, kv_weight, eps, (const float2*)rot, rot_dims, interleaved,
-            slots, (__nv_bfloat16*)cq, (__nv_bfloat16*)cache, q_rank, kv_rank, rot_dim, width);
+            slots, (__nv_bfloat16*)cq, (__nv_bfloat16*)cache, tokens, q_rank, kv_rank, rot_dim, width);
     else
         return mrun_set_error("latent_prepare: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("latent_prepare");
@@ -411,8 +429,14 @@ MRUN_API int mrun_route_top_k(const float* logits, float* weights, int* chosen, 
                  32 * ROUTE_MAX_PER_LANE);
     MRUN_REQUIRE(kind == 0 || kind == 1, "route_top_k: unknown score function %d", kind);
     if (tokens == 0) return 0;
-    route_top_k_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(logits, weights, chosen, tokens, experts, top, kind,
-                                                            renormalize);
+    const dim3 grid((tokens + 3) / 4);
+    if (experts <= 32)
+        route_top_k_kernel<1><<<grid, 128, 0, stream>>>(logits, weights, chosen, tokens, experts, top, kind, renormalize);
+    else if (experts <= 128)
+        route_top_k_kernel<4><<<grid, 128, 0, stream>>>(logits, weights, chosen, tokens, experts, top, kind, renormalize);
+    else
+        route_top_k_kernel<ROUTE_MAX_PER_LANE><<<grid, 128, 0, stream>>>(logits, weights, chosen, tokens, experts, top,
+                                                                        kind, renormalize);
     MRUN_CHECK_LAUNCH("route_top_k");
     return 0;
 }
