@@ -23,58 +23,44 @@ __device__ __forceinline__ void pair_features(int i, int dims, int interleaved, 
 }
 
 // ------------------------------------------------------------------------------------------
-// One warp a token.  down[t] = [query latent (q_rank) | key/value latent (kv_rank) | shared key
+// One block a token.  down[t] = [query latent (q_rank) | key/value latent (kv_rank) | shared key
 // part (rot_dim)], the stacked down-projections' output.  The two latents are RMS-normed with
 // their weights (eps inside the root); the shared key part is not normed, its first `rot_dims`
 // features rotate by the token's table row.  The cache row of width `width` >= kv_rank + rot_dim
 // is filled to its end with zeros, so that an attention kernel may take it as a key of that size.
-// A warp sums in a fixed order (lane-strided, then a butterfly), so a token's result does not
-// depend on the batch; it asks for the norm weights and its table row while the row's values
-// are on their way, and meets no block-wide barrier.
 // ------------------------------------------------------------------------------------------
-constexpr int PREPARE_WARPS = 4;
-
-__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
-
 template <typename TA>
-__global__ void __launch_bounds__(PREPARE_WARPS * 32)
+__global__ void __launch_bounds__(256)
 latent_prepare_kernel(const TA* __restrict__ down, long ld, const float* __restrict__ q_weight,
                       const float* __restrict__ kv_weight, float eps, const float2* __restrict__ rot,
                       int rot_dims, int interleaved, const int* __restrict__ slots, TA* __restrict__ cq,
-                      TA* __restrict__ cache, int tokens, int q_rank, int kv_rank, int rot_dim, int width) {
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * PREPARE_WARPS + (threadIdx.x >> 5);
-    if (t >= tokens) return;
+                      TA* __restrict__ cache, int q_rank, int kv_rank, int rot_dim, int width) {
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, tid = threadIdx.x;
     const TA* row = down + (size_t)t * ld;
     const TA* kv = row + q_rank;
     const int slot = slots ? slots[t] : -1;      // negative: a padding row, or a run that only reads another's cache
-    const int pairs = rot_dims / 2;
+    // both totals of squares from one sweep over the row (measured on B200: a warp a token, and
+    // prefetches of the norm weights during the sweep, were both slower than this)
     float ss_q = 0.f, ss_kv = 0.f;
-    for (int i = lane; i < q_rank; i += 32) {
-        const float v = to_float(row[i]);
-        ss_q += v * v;
-        prefetch_l1(q_weight + i);
-    }
-    if (slot >= 0) {
-        for (int i = lane; i < kv_rank; i += 32) {
-            const float v = to_float(kv[i]);
-            ss_kv += v * v;
-            prefetch_l1(kv_weight + i);
-        }
-        for (int i = lane; i < pairs; i += 32) prefetch_l1(rot + (size_t)t * pairs + i);
-    }
+    for (int i = tid; i < q_rank; i += blockDim.x) { const float v = to_float(row[i]); ss_q += v * v; }
+    if (slot >= 0)
+        for (int i = tid; i < kv_rank; i += blockDim.x) { const float v = to_float(kv[i]); ss_kv += v * v; }
     if (q_rank > 0) {
-        const float inv = rsqrtf(warp_sum(ss_q) / (float)q_rank + eps);
-        for (int i = lane; i < q_rank; i += 32)
+        ss_q = block_sum(ss_q, scratch);
+        const float inv = rsqrtf(ss_q / (float)q_rank + eps);
+        for (int i = tid; i < q_rank; i += blockDim.x)
             cq[(size_t)t * q_rank + i] = from_float<TA>(to_float(row[i]) * inv * q_weight[i]);
     }
     if (slot < 0) return;
-    const float inv = rsqrtf(warp_sum(ss_kv) / (float)kv_rank + eps);
+    ss_kv = block_sum(ss_kv, scratch);
+    const float inv = rsqrtf(ss_kv / (float)kv_rank + eps);
     TA* dst = cache + (size_t)slot * width;
-    for (int i = lane; i < kv_rank; i += 32)
+    for (int i = tid; i < kv_rank; i += blockDim.x)
         dst[i] = from_float<TA>(to_float(kv[i]) * inv * kv_weight[i]);
     const TA* kr = kv + kv_rank;
-    for (int i = lane; i < pairs; i += 32) {
+    const int pairs = rot_dims / 2;
+    for (int i = tid; i < pairs; i += blockDim.x) {
         int a, b;
         pair_features(i, rot_dims, interleaved, a, b);
         const float2 cs = rot[(size_t)t * pairs + i];
@@ -82,8 +68,8 @@ latent_prepare_kernel(const TA* __restrict__ down, long ld, const float* __restr
         dst[kv_rank + a] = from_float<TA>(u * cs.x - v * cs.y);
         dst[kv_rank + b] = from_float<TA>(v * cs.x + u * cs.y);
     }
-    for (int i = rot_dims + lane; i < rot_dim; i += 32) dst[kv_rank + i] = kr[i];
-    for (int i = kv_rank + rot_dim + lane; i < width; i += 32) dst[i] = from_float<TA>(0.f);
+    for (int i = rot_dims + tid; i < rot_dim; i += blockDim.x) dst[kv_rank + i] = kr[i];
+    for (int i = kv_rank + rot_dim + tid; i < width; i += blockDim.x) dst[i] = from_float<TA>(0.f);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -350,15 +336,14 @@ MRUN_API int mrun_latent_prepare(const void* down, int act_dtype, long ld, const
     MRUN_REQUIRE(ld >= q_rank + kv_rank + rot_dim, "latent_prepare: row stride %ld below the row's width", ld);
     MRUN_REQUIRE(rot_dims == 0 || rot != nullptr, "latent_prepare: no rotation table");
     if (tokens == 0) return 0;
-    const int blocks = (tokens + PREPARE_WARPS - 1) / PREPARE_WARPS;
     if (act_dtype == MRUN_F32)
-        latent_prepare_kernel<float><<<blocks, PREPARE_WARPS * 32, 0, stream>>>(
+        latent_prepare_kernel<float><<<tokens, 256, 0, stream>>>(
             (const float*)down, ld, q_weight, kv_weight, eps, (const float2*)rot, rot_dims, interleaved, slots,
-            (float*)cq, (float*)cache, tokens, q_rank, kv_rank, rot_dim, width);
+            (float*)cq, (float*)cache, q_rank, kv_rank, rot_dim, width);
     else if (act_dtype == MRUN_BF16)
-        latent_prepare_kernel<__nv_bfloat16><<<blocks, PREPARE_WARPS * 32, 0, stream>>>(
+        latent_prepare_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
             (const __nv_bfloat16*)down, ld, q_weight, kv_weight, eps, (const float2*)rot, rot_dims, interleaved,
-            slots, (__nv_bfloat16*)cq, (__nv_bfloat16*)cache, tokens, q_rank, kv_rank, rot_dim, width);
+            slots, (__nv_bfloat16*)cq, (__nv_bfloat16*)cache, q_rank, kv_rank, rot_dim, width);
     else
         return mrun_set_error("latent_prepare: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("latent_prepare");

@@ -1,0 +1,155 @@
+// A routed feed-forward's prompt steps: the (token, chosen expert) pairs sorted by expert, so that
+// every expert's rows lie together and a grouped product runs each expert on its own rows only.
+//
+//   moe_count     how many pairs each expert has
+//   moe_place     the experts' row ranges (running totals), and for every pair its row: the row's
+//                 source token and weight, and where each token finds its pairs' rows again
+//   gather_rows   x_sorted[row] = x[source token of row]
+//   relu2_rows    relu(u)^2 times the row's weight
+//   combine_rows  out[t] = base[t] + the rows of token t's pairs, added in the order they were chosen
+//
+// Inside an expert's range the rows stand in the order in which the pairs arrived (an atomic
+// counter); a row's result does not depend on where in the range it stands, and the combine adds
+// a token's rows in a fixed order, so the output has the same bits every run.
+#include "common.cuh"
+
+using namespace mrun;
+
+namespace {
+
+__global__ void moe_count_kernel(const int* __restrict__ chosen, int pairs, int experts, int* __restrict__ counts) {
+    extern __shared__ int local[];
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) local[e] = 0;
+    __syncthreads();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += gridDim.x * blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < experts) atomicAdd(local + e, 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x)
+        if (local[e]) atomicAdd(counts + e, local[e]);
+}
+
+// One block.  ends[e] = pairs of experts 0..e; cursor[e] = where expert e's range starts.
+__global__ void moe_scan_kernel(const int* __restrict__ counts, int experts, int* __restrict__ ends,
+                                int* __restrict__ cursor) {
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int e = 0; e < experts; ++e) {
+            cursor[e] = total;
+            total += counts[e];
+            ends[e] = total;
+        }
+    }
+}
+
+__global__ void moe_place_kernel(const int* __restrict__ chosen, const float* __restrict__ weights, int pairs,
+                                 int experts, int top, int* __restrict__ cursor, int* __restrict__ source,
+                                 float* __restrict__ row_weight, int* __restrict__ dest) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= pairs) return;
+    const int e = chosen[i], t = i / top;
+    const int row = atomicAdd(cursor + e, 1);
+    source[row] = t;
+    row_weight[row] = weights[(size_t)t * experts + e];
+    dest[i] = row;
+}
+
+template <typename TA>
+__global__ void gather_rows_kernel(const TA* __restrict__ x, const int* __restrict__ source, TA* __restrict__ out,
+                                   int width) {
+    const size_t row = blockIdx.x;
+    const TA* src = x + (size_t)source[row] * width;
+    TA* dst = out + row * width;
+    if ((width & 7) == 0 && ((((uintptr_t)x) | ((uintptr_t)out)) & 15) == 0 && sizeof(TA) == 2) {
+        for (int c = threadIdx.x; c < width / 8; c += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+template <typename TA>
+__global__ void relu2_rows_kernel(const TA* __restrict__ u, TA* __restrict__ act, const float* __restrict__ row_weight,
+                                  int width) {
+    const size_t row = blockIdx.x;
+    const float w = row_weight[row];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = fmaxf(to_float(u[row * width + c]), 0.f);
+        act[row * width + c] = from_float<TA>(v * v * w);
+    }
+}
+
+template <typename TA, typename TB>
+__global__ void combine_rows_kernel(const TB* __restrict__ base, const TA* __restrict__ rows,
+                                    const int* __restrict__ dest, float* __restrict__ out, int top, int width) {
+    const size_t t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float s = base ? to_float(base[t * width + c]) : 0.f;
+        for (int k = 0; k < top; ++k) s += to_float(rows[(size_t)dest[t * top + k] * width + c]);
+        out[t * width + c] = s;
+    }
+}
+
+}  // namespace
+
+// counts, ends, cursor: int32 [experts] (counts zeroed by the caller); source, row_weight: [pairs];
+// dest: [pairs] (= [tokens, top]).
+MRUN_API int mrun_moe_sort(const int* chosen, const float* weights, int tokens, int experts, int top, int* counts,
+                           int* ends, int* cursor, int* source, float* row_weight, int* dest, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && experts > 0 && experts <= 4096 && top > 0 && top <= experts,
+                 "moe_sort: bad sizes tokens=%d experts=%d top=%d", tokens, experts, top);
+    const long pairs = (long)tokens * top;
+    MRUN_REQUIRE(pairs < (1L << 31), "moe_sort: %ld pairs exceed the supported 2^31", pairs);
+    if (pairs == 0) return 0;
+    const int blocks = (int)((pairs + 255) / 256);
+    moe_count_kernel<<<blocks < 512 ? blocks : 512, 256, experts * sizeof(int), stream>>>(chosen, (int)pairs, experts, counts);
+    MRUN_CHECK_LAUNCH("moe_sort (count)");
+    moe_scan_kernel<<<1, 32, 0, stream>>>(counts, experts, ends, cursor);
+    MRUN_CHECK_LAUNCH("moe_sort (scan)");
+    moe_place_kernel<<<blocks, 256, 0, stream>>>(chosen, weights, (int)pairs, experts, top, cursor, source, row_weight, dest);
+    MRUN_CHECK_LAUNCH("moe_sort (place)");
+    return 0;
+}
+
+MRUN_API int mrun_gather_rows(const void* x, int act_dtype, const int* source, void* out, int rows, int width,
+                              cudaStream_t stream) {
+    MRUN_REQUIRE(rows >= 0 && width > 0, "gather_rows: bad sizes rows=%d width=%d", rows, width);
+    if (rows == 0) return 0;
+    if (act_dtype == MRUN_BF16)
+        gather_rows_kernel<__nv_bfloat16><<<rows, 128, 0, stream>>>((const __nv_bfloat16*)x, source, (__nv_bfloat16*)out, width);
+    else if (act_dtype == MRUN_F32)
+        gather_rows_kernel<float><<<rows, 128, 0, stream>>>((const float*)x, source, (float*)out, width);
+    else
+        return mrun_set_error("gather_rows: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("gather_rows");
+    return 0;
+}
+
+MRUN_API int mrun_relu2_rows(const void* u, void* act, int act_dtype, const float* row_weight, int rows, int width,
+                             cudaStream_t stream) {
+    MRUN_REQUIRE(rows >= 0 && width > 0, "relu2_rows: bad sizes rows=%d width=%d", rows, width);
+    if (rows == 0) return 0;
+    if (act_dtype == MRUN_BF16)
+        relu2_rows_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)act, row_weight, width);
+    else if (act_dtype == MRUN_F32)
+        relu2_rows_kernel<float><<<rows, 256, 0, stream>>>((const float*)u, (float*)act, row_weight, width);
+    else
+        return mrun_set_error("relu2_rows: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("relu2_rows");
+    return 0;
+}
+
+// base: [tokens, width] in the activation dtype (base_f32 = 0) or float32 (1), or null.
+MRUN_API int mrun_combine_rows(const void* base, int base_f32, const void* rows, int act_dtype, const int* dest,
+                               float* out, int tokens, int top, int width, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && top > 0 && width > 0, "combine_rows: bad sizes tokens=%d top=%d width=%d", tokens, top, width);
+    MRUN_REQUIRE(act_dtype == MRUN_BF16, "combine_rows: the sorted path runs in bfloat16");
+    if (tokens == 0) return 0;
+    if (base_f32)
+        combine_rows_kernel<__nv_bfloat16, float><<<tokens, 256, 0, stream>>>((const float*)base, (const __nv_bfloat16*)rows, dest, out, top, width);
+    else
+        combine_rows_kernel<__nv_bfloat16, __nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)base, (const __nv_bfloat16*)rows, dest, out, top, width);
+    MRUN_CHECK_LAUNCH("combine_rows");
+    return 0;
+}

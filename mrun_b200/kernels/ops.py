@@ -734,3 +734,69 @@ def soft_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
     _check(x, "x", torch.float32)
     _lib.core().call("mrun_soft_cap", _ptr(x), _c_long(x.numel()), _c_float(cap), _stream())
     return x
+
+
+# ------------------------------------------------------------------ a routed feed-forward's rows sorted by expert
+
+def moe_sort(chosen: torch.Tensor, weights: torch.Tensor):
+    """Sorts the (token, chosen expert) pairs by expert.  ``chosen``: int32 [tokens, top];
+    ``weights``: float32 [tokens, experts].  Returns ``ends`` (int32 [experts]: where each expert's
+    rows end), ``source`` (int32 [pairs]: the token of every row), ``row_weight`` (float32
+    [pairs]) and ``dest`` (int32 [tokens, top]: the row of every pair)."""
+    _check(chosen, "chosen", torch.int32); _check(weights, "weights", torch.float32)
+    tokens, top = chosen.shape
+    experts = weights.shape[1]
+    if weights.shape[0] != tokens:
+        raise KernelError(f"moe_sort: chosen {tuple(chosen.shape)} vs weights {tuple(weights.shape)}")
+    dev = chosen.device
+    books = torch.zeros((3, experts), dtype=torch.int32, device=dev)          # counts, ends, cursor
+    source = torch.empty(tokens * top, dtype=torch.int32, device=dev)
+    row_weight = torch.empty(tokens * top, dtype=torch.float32, device=dev)
+    dest = torch.empty((tokens, top), dtype=torch.int32, device=dev)
+    _lib.core().call("mrun_moe_sort", _ptr(chosen), _ptr(weights), _c_int(tokens), _c_int(experts), _c_int(top),
+                     _ptr(books[0]), _ptr(books[1]), _ptr(books[2]), _ptr(source), _ptr(row_weight), _ptr(dest), _stream())
+    return books[1], source, row_weight, dest
+
+
+def gather_rows(x: torch.Tensor, source: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[source[r]]."""
+    _check(x, "x"); _check(source, "source", torch.int32)
+    out = torch.empty((source.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _lib.core().call("mrun_gather_rows", _ptr(x), dtype_code(x.dtype), _ptr(source), _ptr(out), _c_int(source.numel()),
+                     _c_int(x.shape[1]), _stream())
+    return out
+
+
+def relu2_rows(u: torch.Tensor, row_weight: torch.Tensor) -> torch.Tensor:
+    """relu(u)^2 times the row's weight."""
+    _check(u, "u"); _check(row_weight, "row_weight", torch.float32)
+    if row_weight.numel() != u.shape[0]:
+        raise KernelError("relu2_rows: one weight per row is needed")
+    act = torch.empty_like(u)
+    _lib.core().call("mrun_relu2_rows", _ptr(u), _ptr(act), dtype_code(u.dtype), _ptr(row_weight), _c_int(u.shape[0]),
+                     _c_int(u.shape[1]), _stream())
+    return act
+
+
+def combine_rows(base: Optional[torch.Tensor], rows: torch.Tensor, dest: torch.Tensor) -> torch.Tensor:
+    """float32 out[t] = base[t] + sum over k of rows[dest[t, k]], added in the order of k."""
+    _check(rows, "rows", torch.bfloat16); _check(dest, "dest", torch.int32)
+    tokens, top = dest.shape
+    width = rows.shape[1]
+    if base is not None:
+        _check(base, "base")
+        if base.shape != (tokens, width) or base.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError(f"combine_rows: base {tuple(base.shape)} {base.dtype}")
+    out = torch.empty((tokens, width), dtype=torch.float32, device=rows.device)
+    _lib.core().call("mrun_combine_rows", _ptr(base), _c_int(1 if base is not None and base.dtype == torch.float32 else 0),
+                     _ptr(rows), dtype_code(rows.dtype), _ptr(dest), _ptr(out), _c_int(tokens), _c_int(top),
+                     _c_int(width), _stream())
+    return out
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:
+    """y[r] = x[r] @ w[g].T for the rows r of group g (rows ends[g-1] .. ends[g]): the vendor
+    library's grouped product in bfloat16 with 32-bit sums.  ``w``: [groups, out, in], which may
+    be a strided view as long as ``in`` has unit stride."""
+    _check(x, "x", torch.bfloat16); _check(w, "w", torch.bfloat16, dense=False); _check(ends, "ends", torch.int32)
+    return torch.nn.functional.grouped_mm(x, w.transpose(-2, -1), offs=ends)

@@ -9,6 +9,14 @@ product up, one kernel that applies relu^2 and the token's weight of the column'
 for an expert the token did not choose, one for the shared expert), and one product down, which
 sums the weighted experts and the shared expert in its 32-bit accumulator.  Every token's result
 depends on its own row only.
+
+A prompt step in bfloat16 (``SORT_MIN_TOKENS`` rows or more) computes only the experts a token
+chose: the (token, expert) pairs are sorted by expert (``ops.moe_sort``), the tokens' rows gathered
+in that order, both products run as grouped products over the experts' row ranges with relu^2 and
+the row's weight between them, and one kernel adds each token's rows, in the order its experts
+were chosen, to the shared expert's output.  Steps of fewer rows, and the 32-bit path, compute
+every expert with zero weights as above: with a handful of rows most experts' weights are read
+either way, and the 32-bit path keeps one summation order for every cutting.
 """
 from __future__ import annotations
 
@@ -19,6 +27,7 @@ from ..kernels import ops
 from .base import Runtime, register_feed_forward
 
 ACTIVATIONS = ("relu2",)
+SORT_MIN_TOKENS = 64        # rows of a step from which the pairs are sorted by expert (bfloat16)
 
 
 @register_feed_forward("routed_mlp")
@@ -46,13 +55,38 @@ class RoutedMLP:
         self.w_router = runtime.matrix(tensors["router"])
         self.w_up = runtime.matrix(torch.cat([tensors[f"{n}.up"] for n in names], dim=0))
         self.w_down = runtime.matrix(torch.cat([tensors[f"{n}.down"] for n in names], dim=1))
+        # the same memory seen expert by expert, for the grouped products: [experts, out, in]
+        routed = spec.experts * spec.expert_ff
+        self.w_up_experts = self.w_up[:routed].view(spec.experts, spec.expert_ff, spec.hidden)
+        self.w_down_experts = self.w_down[:, :routed].view(spec.hidden, spec.experts, spec.expert_ff).permute(1, 0, 2)
+        self.w_up_shared = self.w_up[routed:] if spec.shared_ff else None
+        self.w_down_shared = self.w_down[:, routed:] if spec.shared_ff else None
+        self.sortable = (runtime.precision.act == torch.bfloat16 and spec.top < spec.experts
+                         and spec.hidden % 8 == 0 and spec.expert_ff % 8 == 0 and self.w_down.shape[1] % 8 == 0)
 
     def activation_elements(self) -> int:
         return 2 * (self.spec.experts * self.spec.expert_ff + self.spec.shared_ff) + self.spec.experts
 
+    def _sorted_forward(self, x, logits):
+        """Only the chosen experts: float32 [tokens, hidden]."""
+        s = self.spec
+        chosen = torch.empty((x.shape[0], s.top), dtype=torch.int32, device=x.device)
+        weights = ops.route_top_k(logits, s.top, s.score, s.renormalize, chosen=chosen)
+        ends, source, row_weight, dest = ops.moe_sort(chosen, weights)
+        rows = ops.gather_rows(x, source)
+        act = ops.relu2_rows(ops.grouped_linear(rows, self.w_up_experts, ends), row_weight)
+        rows = ops.grouped_linear(act, self.w_down_experts, ends)
+        base = None
+        if s.shared_ff:
+            shared = ops.relu2_scaled(ops.linear(x, self.w_up_shared), None, 0, 1)
+            base = torch.mm(shared, self.w_down_shared.t(), out_dtype=torch.float32)
+        return ops.combine_rows(base, rows, dest)
+
     def forward(self, x, ctx, defer_output: bool = False):
         s = self.spec
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
+        if self.sortable and x.shape[0] >= SORT_MIN_TOKENS and not torch.cuda.is_current_stream_capturing():
+            return self._sorted_forward(x, logits)
         weights = ops.route_top_k(logits, s.top, s.score, s.renormalize)
         act = ops.relu2_scaled(ops.linear(x, self.w_up), weights, s.experts, s.expert_ff)
         if defer_output:

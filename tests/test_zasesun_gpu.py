@@ -242,11 +242,15 @@ def test_routed_feed_forward_part(experts, top, shared, dtype):
     spec = RoutedMLPSpec(hidden=72, experts=experts, top=top, expert_ff=24, shared_ff=shared)
     tensors = random_part_tensors(FEED_FORWARDS.tensor_specs(spec, "f"), 11, std=0.2)
     part = FEED_FORWARDS.build(spec, {k[2:]: v for k, v in tensors.items()}, rt)
-    h = torch.randn(50, 72, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    # 300 rows: in bfloat16 a step of this size sorts its rows by expert and runs grouped products
+    h = torch.randn(300, 72, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
     mlp = {"router": {"experts": experts, "top": top}, "shared": {"ff": shared} if shared else None}
     want = plain.routed_feed_forward(h.to(F64), tensors, "f", mlp)
     got = part.forward(h.to(DEV, rt.precision.act), None)
     close(got, want, dtype, "all rows")
+    assert part.sortable == (dtype == "bfloat16" and top < experts)
+    again = part.forward(h.to(DEV, rt.precision.act), None)
+    assert torch.equal(again, got), "the same step twice must give the same bits"
     for rows in ([0], [7, 8], list(range(20, 37))):               # a row's result is its own
         alone = part.forward(h[rows].to(DEV, rt.precision.act), None)
         close(alone, want[rows], dtype, f"rows {rows[:3]}")
