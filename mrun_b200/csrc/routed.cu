@@ -69,25 +69,56 @@ __global__ void gather_rows_kernel(const TA* __restrict__ x, const int* __restri
     }
 }
 
-template <typename TA>
+// VEC: eight values a thread and step (the width a multiple of 8, the pointers on 16 bytes).
+template <typename TA, bool VEC>
 __global__ void relu2_rows_kernel(const TA* __restrict__ u, TA* __restrict__ act, const float* __restrict__ row_weight,
                                   int width) {
     const size_t row = blockIdx.x;
     const float w = row_weight[row];
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float v = fmaxf(to_float(u[row * width + c]), 0.f);
-        act[row * width + c] = from_float<TA>(v * v * w);
+    if constexpr (VEC) {
+        for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+            float v[8];
+            Vec8<TA>::load(u + row * width + c, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float x = fmaxf(v[i], 0.f);
+                v[i] = x * x * w;
+            }
+            Vec8<TA>::store(act + row * width + c, v);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            const float v = fmaxf(to_float(u[row * width + c]), 0.f);
+            act[row * width + c] = from_float<TA>(v * v * w);
+        }
     }
 }
 
-template <typename TA, typename TB>
+template <typename TA, typename TB, bool VEC>
 __global__ void combine_rows_kernel(const TB* __restrict__ base, const TA* __restrict__ rows,
                                     const int* __restrict__ dest, float* __restrict__ out, int top, int width) {
     const size_t t = blockIdx.x;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float s = base ? to_float(base[t * width + c]) : 0.f;
-        for (int k = 0; k < top; ++k) s += to_float(rows[(size_t)dest[t * top + k] * width + c]);
-        out[t * width + c] = s;
+    if constexpr (VEC) {
+        for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+            float s[8];
+            if (base) Vec8<TB>::load(base + t * width + c, s);
+            else
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s[i] = 0.f;
+            for (int k = 0; k < top; ++k) {
+                float r[8];
+                Vec8<TA>::load(rows + (size_t)dest[t * top + k] * width + c, r);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s[i] += r[i];
+            }
+            Vec8<float>::store(out + t * width + c, s);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float s = base ? to_float(base[t * width + c]) : 0.f;
+            for (int k = 0; k < top; ++k) s += to_float(rows[(size_t)dest[t * top + k] * width + c]);
+            out[t * width + c] = s;
+        }
     }
 }
 
@@ -130,10 +161,13 @@ MRUN_API int mrun_relu2_rows(const void* u, void* act, int act_dtype, const floa
                              cudaStream_t stream) {
     MRUN_REQUIRE(rows >= 0 && width > 0, "relu2_rows: bad sizes rows=%d width=%d", rows, width);
     if (rows == 0) return 0;
-    if (act_dtype == MRUN_BF16)
-        relu2_rows_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)act, row_weight, width);
+    const bool vec = width % 8 == 0 && ((((uintptr_t)u) | ((uintptr_t)act)) & 15) == 0;
+    if (act_dtype == MRUN_BF16 && vec)
+        relu2_rows_kernel<__nv_bfloat16, true><<<rows, 128, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)act, row_weight, width);
+    else if (act_dtype == MRUN_BF16)
+        relu2_rows_kernel<__nv_bfloat16, false><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)act, row_weight, width);
     else if (act_dtype == MRUN_F32)
-        relu2_rows_kernel<float><<<rows, 256, 0, stream>>>((const float*)u, (float*)act, row_weight, width);
+        relu2_rows_kernel<float, false><<<rows, 256, 0, stream>>>((const float*)u, (float*)act, row_weight, width);
     else
         return mrun_set_error("relu2_rows: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("relu2_rows");
@@ -146,10 +180,16 @@ MRUN_API int mrun_combine_rows(const void* base, int base_f32, const void* rows,
     MRUN_REQUIRE(tokens >= 0 && top > 0 && width > 0, "combine_rows: bad sizes tokens=%d top=%d width=%d", tokens, top, width);
     MRUN_REQUIRE(act_dtype == MRUN_BF16, "combine_rows: the sorted path runs in bfloat16");
     if (tokens == 0) return 0;
-    if (base_f32)
-        combine_rows_kernel<__nv_bfloat16, float><<<tokens, 256, 0, stream>>>((const float*)base, (const __nv_bfloat16*)rows, dest, out, top, width);
+    const bool vec = width % 8 == 0 && ((((uintptr_t)base) | ((uintptr_t)rows) | ((uintptr_t)out)) & 15) == 0;
+    using bf16 = __nv_bfloat16;
+    if (base_f32 && vec)
+        combine_rows_kernel<bf16, float, true><<<tokens, 128, 0, stream>>>((const float*)base, (const bf16*)rows, dest, out, top, width);
+    else if (base_f32)
+        combine_rows_kernel<bf16, float, false><<<tokens, 256, 0, stream>>>((const float*)base, (const bf16*)rows, dest, out, top, width);
+    else if (vec)
+        combine_rows_kernel<bf16, bf16, true><<<tokens, 128, 0, stream>>>((const bf16*)base, (const bf16*)rows, dest, out, top, width);
     else
-        combine_rows_kernel<__nv_bfloat16, __nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)base, (const __nv_bfloat16*)rows, dest, out, top, width);
+        combine_rows_kernel<bf16, bf16, false><<<tokens, 256, 0, stream>>>((const bf16*)base, (const bf16*)rows, dest, out, top, width);
     MRUN_CHECK_LAUNCH("combine_rows");
     return 0;
 }

@@ -70,9 +70,10 @@ class Model:
         def walk(obj):
             nonlocal total
             if isinstance(obj, torch.Tensor):
-                if obj.data_ptr() not in seen:
-                    seen.add(obj.data_ptr())
-                    total += obj.numel() * obj.element_size()
+                storage = obj.untyped_storage()         # views of one tensor share it and count once
+                if storage.data_ptr() not in seen:
+                    seen.add(storage.data_ptr())
+                    total += storage.nbytes()
             elif hasattr(obj, "__dict__"):
                 for value in vars(obj).values():
                     if isinstance(value, (torch.Tensor,)) or hasattr(value, "__dict__"):

@@ -722,7 +722,7 @@ def relu2_scaled(u: torch.Tensor, weights: Optional[torch.Tensor], experts: int,
         if weights.shape != (tokens, experts):
             raise KernelError(f"relu2_scaled: weights {tuple(weights.shape)}, expected {(tokens, experts)}")
     else:
-        experts = 0
+        experts, ff = 0, columns
     act = torch.empty_like(u)
     _lib.core().call("mrun_relu2_scaled", _ptr(u), _ptr(act), dtype_code(u.dtype), _ptr(weights), _c_int(tokens),
                      _c_int(columns), _c_int(experts), _c_int(max(1, ff)), _stream())

@@ -10,15 +10,21 @@ for an expert the token did not choose, one for the shared expert), and one prod
 sums the weighted experts and the shared expert in its 32-bit accumulator.  Every token's result
 depends on its own row only.
 
-A prompt step in bfloat16 (``SORT_MIN_TOKENS`` rows or more) computes only the experts a token
-chose: the (token, expert) pairs are sorted by expert (``ops.moe_sort``), the tokens' rows gathered
+A bfloat16 step that would spend ``SORT_MIN_SAVED_FLOPS`` or more on experts nobody chose computes
+only the experts a token chose: the (token, expert) pairs are sorted by expert (``ops.moe_sort``), the tokens' rows gathered
 in that order, both products run as grouped products over the experts' row ranges with relu^2 and
 the row's weight between them, and one kernel adds each token's rows, in the order its experts
-were chosen, to the shared expert's output.  Steps of fewer rows, and the 32-bit path, compute
-every expert with zero weights as above: with a handful of rows most experts' weights are read
-either way, and the 32-bit path keeps one summation order for every cutting.
+were chosen, to the shared expert's output.  Smaller steps, and the 32-bit path, compute every
+expert with zero weights as above: the sort, the gather and the grouped products' set-up cost a few
+hundred microseconds of a step (measured on B200: at 2,048 rows, width 2,048 and 8 experts of
+2,048 of which 2 are chosen the sorted step loses, at width 4,096 and experts of 3,072 it wins),
+with a handful of rows most experts' weights are read either way, and the 32-bit path keeps one
+summation order for every cutting.  ``MRUN_MOE_SORT_MIN_FLOPS`` in the environment overrides the
+threshold (0: every bfloat16 step sorts).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -27,7 +33,8 @@ from ..kernels import ops
 from .base import Runtime, register_feed_forward
 
 ACTIVATIONS = ("relu2",)
-SORT_MIN_TOKENS = 64        # rows of a step from which the pairs are sorted by expert (bfloat16)
+# FLOPs a step would spend on experts nobody chose, from which its pairs are sorted by expert
+SORT_MIN_SAVED_FLOPS = float(os.environ.get("MRUN_MOE_SORT_MIN_FLOPS", 4e11))
 
 
 @register_feed_forward("routed_mlp")
@@ -85,7 +92,9 @@ class RoutedMLP:
     def forward(self, x, ctx, defer_output: bool = False):
         s = self.spec
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
-        if self.sortable and x.shape[0] >= SORT_MIN_TOKENS and not torch.cuda.is_current_stream_capturing():
+        saved = 4.0 * x.shape[0] * (s.experts - s.top) * s.expert_ff * s.hidden
+        if self.sortable and saved >= SORT_MIN_SAVED_FLOPS and x.shape[0] > 16 \
+                and not torch.cuda.is_current_stream_capturing():
             return self._sorted_forward(x, logits)
         weights = ops.route_top_k(logits, s.top, s.score, s.renormalize)
         act = ops.relu2_scaled(ops.linear(x, self.w_up), weights, s.experts, s.expert_ff)

@@ -235,14 +235,15 @@ def test_one_key_stands_out(name, page_size, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("experts, top, shared", [(5, 2, 16), (3, 1, 0), (4, 4, 8), (40, 6, 0)])
-def test_routed_feed_forward_part(experts, top, shared, dtype):
+def test_routed_feed_forward_part(experts, top, shared, dtype, monkeypatch):
     from mrun_b200.config import RoutedMLPSpec
-    from mrun_b200.parts import FEED_FORWARDS
+    from mrun_b200.parts import FEED_FORWARDS, routed
     rt = runtime(dtype)
     spec = RoutedMLPSpec(hidden=72, experts=experts, top=top, expert_ff=24, shared_ff=shared)
     tensors = random_part_tensors(FEED_FORWARDS.tensor_specs(spec, "f"), 11, std=0.2)
     part = FEED_FORWARDS.build(spec, {k[2:]: v for k, v in tensors.items()}, rt)
-    # 300 rows: in bfloat16 a step of this size sorts its rows by expert and runs grouped products
+    # in bfloat16 the step sorts its rows by expert and runs grouped products over the chosen ones
+    monkeypatch.setattr(routed, "SORT_MIN_SAVED_FLOPS", 0.0)
     h = torch.randn(300, 72, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
     mlp = {"router": {"experts": experts, "top": top}, "shared": {"ff": shared} if shared else None}
     want = plain.routed_feed_forward(h.to(F64), tensors, "f", mlp)
@@ -251,6 +252,10 @@ def test_routed_feed_forward_part(experts, top, shared, dtype):
     assert part.sortable == (dtype == "bfloat16" and top < experts)
     again = part.forward(h.to(DEV, rt.precision.act), None)
     assert torch.equal(again, got), "the same step twice must give the same bits"
+    if part.sortable:                  # and the step that computes every expert agrees
+        monkeypatch.setattr(routed, "SORT_MIN_SAVED_FLOPS", 1e30)
+        close(part.forward(h.to(DEV, rt.precision.act), None), want, dtype, "all rows, every expert computed")
+        monkeypatch.setattr(routed, "SORT_MIN_SAVED_FLOPS", 0.0)
     for rows in ([0], [7, 8], list(range(20, 37))):               # a row's result is its own
         alone = part.forward(h[rows].to(DEV, rt.precision.act), None)
         close(alone, want[rows], dtype, f"rows {rows[:3]}")
@@ -318,8 +323,10 @@ def plain_logits(cfg, weights, tokens):
     return logits, close_call
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_every_cutting_matches_plain(ztiny, dtype, tmp_path):
+@pytest.mark.parametrize("dtype, sorted_experts", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_every_cutting_matches_plain(ztiny, dtype, sorted_experts, tmp_path, monkeypatch):
+    """``sorted_experts``: the routed layers' steps of more than 16 rows sort their rows by expert
+    and compute the chosen experts only; else every step computes all experts."""
     name, folder, settings = ztiny
     cfg, weights = load_folder(folder)
     vocab = cfg["vocab"]
@@ -347,6 +354,7 @@ def test_every_cutting_matches_plain(ztiny, dtype, tmp_path):
     section("end")
     # four live requests, each rounded up to 64 tokens: so few pages that they are used again
     rounded = sorted((-(-n // 64) * 64 for n in LENGTHS), reverse=True)
+    monkeypatch.setenv("MRUN_MOE_SORT_MIN_FLOPS", "0" if sorted_experts else "1e30")
     runner = TraceRunner(folder, dtype, str(tmp_path / "out"), sum(rounded[:4]), settings["page_size"], max_requests=4)
     try:
         runner.run(b.steps)
