@@ -242,7 +242,7 @@ def _zasesun_sizes(width, heads, dim, rot_dim, vdim, q_rank, kv_rank, ff, expert
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff},
            "shared": {"ff": shared_ff}}
-    return {"architecture": "Zasesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+    return {"architecture": "Zasesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
             "logit_softcap": 30.0,
             "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe}
                        for i in range(layers)]}
