@@ -1,5 +1,5 @@
 """Small Zasesun configurations for the tests, none like another: layers of one model differ in
-their head counts, latent ranks and rotary settings; cache rows of 48, 64, 128 and 272 features
+their head counts, latent ranks and rotary settings; cache rows of 32, 48, 64, 128 and 272 features
 (the mma.sync, TMA / tcgen05 and CUDA-core attention kernels); dense, routed and absent
 feed-forwards; one to all experts chosen; with and without a shared expert, a stretch of the
 rotary frequencies, a soft cap; residual multipliers on both sides of one."""
@@ -63,6 +63,15 @@ ZTINY = {
                                  moe(4, 4, 24, shared=8)),
                            layer(mixer(1, 48, 32, 56, 8, 24, 0.2), dense(72))]},
         seed=9, std=0.1, norm_noise=0.3, page_size=4),
+    # sizes that fit no vector width or alignment: an odd width, latent ranks and head sizes that are
+    # no multiple of 8, seven heads, three of seven experts of an odd size, an odd vocabulary
+    "S": dict(
+        config={"architecture": "Zasesun", "vocab": 131, "width": 100, "norm": {"eps": 1e-5}, "residual_mult": 0.9,
+                "logit_softcap": 5.0,
+                "layers": [layer(mixer(7, 10, 6, 14, 18, 50, 0.35, base=3000.0, scaling=(3.0, 48, 6.0, 1.5)),
+                                 moe(7, 3, 22, shared=12)),
+                           layer(mixer(3, 12, 10, 6, 30, 21, 0.3, base=700.0), dense(90))]},
+        seed=13, std=0.1, norm_noise=0.2, page_size=16),
 }
 
 
