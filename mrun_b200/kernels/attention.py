@@ -210,14 +210,31 @@ def decode_fuses_input(ctx, dtype: torch.dtype, heads: int, kv_heads: int, head_
     return ctx.all_decode and ratio <= 16 and supports_tensor_cores(dtype, head_dim, ratio)
 
 
+def latent_wide_ok(dtype: torch.dtype, width: int, value_dim: int) -> bool:
+    """Whether the tensor-core kernel for wide latent rows takes this shape (bfloat16, rows of a
+    multiple of 16 features, at most 512 value columns)."""
+    return dtype == torch.bfloat16 and bool(_lib.core()._dll.mrun_latent_attention_wide_ok(_c_int(width), _c_int(value_dim)))
+
+
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, group, ctx,
-                    heads: int, scale: float, window: int, raw=None) -> torch.Tensor:
+                    heads: int, scale: float, window: int, raw=None, value_dim: int = 0) -> torch.Tensor:
     """``q``: the step's queries (row t at ``q_stride * t``, heads contiguous); ``cache``: the
     schedule entry's pages; ``group``: the step's view of the cache's group.  ``raw``, only where
     :func:`decode_fuses_input` holds: ``(q_weight, k_weight, eps, rot, rotary_dim, slots)`` for a
-    ``q`` that is the projection's raw [q | k | v] rows."""
+    ``q`` that is the projection's raw [q | k | v] rows.  ``value_dim``, for a cache whose rows
+    are key and value at once (one tensor of pages, one kv head): how many of a row's first
+    features the caller reads of the output; rows too wide for the per-head-size kernels then go
+    to the kernel for wide latent rows."""
     pages, kv_heads, page_size, head_dim = cache.k.shape
     ratio = heads // kv_heads
+    if (value_dim and cache.v is cache.k and kv_heads == 1 and window == 0 and raw is None
+            and not supports_tensor_cores(q.dtype, head_dim, ratio) and latent_wide_ok(q.dtype, head_dim, value_dim)):
+        ops._check(q, "q", torch.bfloat16, dense=False); ops._check(out, "out", torch.bfloat16)
+        _lib.core().call("mrun_latent_attention_wide", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(cache.k),
+                         _ptr(group.block_tables), _c_int(group.max_blocks), _ptr(ctx.token_slot), _ptr(ctx.positions),
+                         _c_int(ctx.num_tokens), _c_int(heads), _c_int(head_dim), _c_int(value_dim), _c_int(page_size),
+                         _c_long(pages * page_size), _c_float(scale), _stream())
+        return out
     if not supports_tensor_cores(q.dtype, head_dim, ratio):
         return ops.paged_attention_generic(q, q_stride, out, cache.k, cache.v, group.block_tables,
                                            ctx.token_slot, ctx.positions, heads, scale, window)

@@ -184,7 +184,7 @@ def build_host() -> str:
 
 
 CORE_SOURCES = ("common.cu", "elementwise.cu", "latent.cu", "routed.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc5.cu",
-                "attention_generic.cu", "sampling.cu")
+                "attention_generic.cu", "attention_latent.cu", "sampling.cu")
 
 
 def build_core() -> str:

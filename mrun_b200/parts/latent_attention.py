@@ -11,7 +11,9 @@ so the query row ``[U_h^T q_plain | q_rot | 0...]`` meets the cache row as one k
 key/value head, and the head's output is W_h (sum_j p_j c_j): the same cache row is the value,
 and W_h runs on the weighted latent.  The framework's paged attention kernels therefore serve
 this mixer unchanged (``heads`` query heads over one kv head whose K and V are the same pages);
-prefill, decode and mixed steps take the paths they take for grouped-query attention.
+prefill, decode and mixed steps take the paths they take for grouped-query attention.  Rows wider
+than those kernels' 256 features (a latent of 512, say) go to a tensor-core kernel of their own
+(``csrc/attention_latent.cu``: a block a token and 16 heads, a quarter of the value columns a warp).
 
 Per step: one product for both down-projections (their weights stacked), one kernel that norms
 the two latents, rotates r and writes the cache row, the query up-projection, a per-head product
@@ -91,7 +93,7 @@ class LatentAttention:
         ops.latent_query(q, rot, self.rot_dims, self.pairing, q_att, s.heads, s.dim, s.rot_dim, s.kv_rank)
         mixed = torch.empty((tokens, s.heads * width), dtype=x.dtype, device=x.device)
         paged_attention(q_att.view(tokens, s.heads * width), s.heads * width, mixed, cache, group, ctx, s.heads,
-                        s.softmax_scale, 0)
+                        s.softmax_scale, 0, value_dim=s.kv_rank)
         value = torch.empty((tokens, s.heads, s.vdim), dtype=x.dtype, device=x.device)
         ops.linear_per_head(mixed.view(tokens, s.heads, width)[:, :, :s.kv_rank], self.w_uv, value)
         value = value.view(tokens, s.heads * s.vdim)

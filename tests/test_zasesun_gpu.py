@@ -159,6 +159,8 @@ MIXERS = {
     "row64": (3, 32, 16, 16, 40, 48, 0.3, (16, 500.0, (4.0, 64.0, 8.0, 2.0))),
     "row128": (4, 24, 16, 40, 56, 112, 0.3, (16, 10000.0, (2.0, 32.0, 4.0, 0.5))),
     "row272_20heads": (20, 8, 8, 8, 32, 264, 0.4, (8, 50.0, None)),
+    "row576": (16, 24, 64, 16, 32, 512, 0.2, (64, 10000.0, (4.0, 256.0, 32.0, 1.0))),
+    "row304_3heads": (3, 16, 16, 24, 24, 280, 0.3, (16, 200.0, None)),
     "partly_rotated": (2, 16, 16, 8, 16, 24, 0.4, (8, 30.0, None)),
 }
 
@@ -206,7 +208,8 @@ def test_latent_attention_part(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name, page_size", [("row64", 16), ("row128", 8), ("row48", 4), ("row272_20heads", 16)])
+@pytest.mark.parametrize("name, page_size", [("row64", 16), ("row128", 8), ("row48", 4), ("row272_20heads", 16),
+                                             ("row576", 16), ("row304_3heads", 4)])
 def test_one_key_stands_out(name, page_size, dtype):
     """The shared rotated key part is not normed, so a token whose input is scaled up has a key that
     dominates (or is shut out of) every head's softmax, wherever it sits: among the first tokens,
