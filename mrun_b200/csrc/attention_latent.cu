@@ -11,8 +11,9 @@
 //   softmax     eight threads a row: running maximum and total in 32-bit, P as bfloat16
 //   O += P V    warp w keeps a quarter of the value columns in registers (up to 128 columns,
 //               so value_cols <= 512) and reads V from the same tile of shared memory
-// Keys outside the token's range are copied as zeros, so a masked key adds exactly nothing.  The
-// order of the additions depends on the token's own keys only.
+// Keys outside the token's range are copied as zeros, so a masked key adds exactly nothing.  A
+// step of few tokens deals every token's tiles to several blocks (grid.z), which leave their
+// unnormalised sums in scratch for a merge kernel that adds them in a fixed order.
 #include "attention_paging.cuh"
 #include "common.cuh"
 
@@ -22,6 +23,7 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 constexpr int TILE_KEYS = 32, ROWS = 16, THREADS = 128, MAX_TILES_A_WARP = 16;
+constexpr int MIN_RUN = 8;          // the fewest key tiles a block of a split launch takes
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -45,13 +47,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid: (tokens, head groups of 16).  `tokens_rows` (nullable): the rows of q and out that the
-// grid's tokens stand for, with their positions and slots in `positions` and `token_slot`.
+// grid: (tokens, head groups of 16, splits).
 __global__ void __launch_bounds__(THREADS)
 latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, const bf16* __restrict__ cache,
                    const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
                    const int* __restrict__ positions, int heads, int width, int value_cols, int page_size,
-                   int page_shift, float scale) {
+                   int page_shift, float scale, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int ld = width + 8;                                   // row stride in elements: an odd number of 16-byte chunks
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [ROWS][ld]
@@ -87,8 +88,15 @@ latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__
         }
     };
 
-    const int tiles = pos / TILE_KEYS + 1;
-    load_tile(0, 0);
+    // with `splits` > 1 the token's tiles are dealt to gridDim.z blocks in equal runs; a block
+    // leaves its unnormalised sums, maxima and totals in the scratch arrays for the merge kernel
+    const int all_tiles = pos / TILE_KEYS + 1;
+    // at least MIN_RUN tiles a block: a captured step is launched with the splits of its longest
+    // possible context, and a shorter token leaves the later blocks without tiles (an empty piece)
+    const int run = max((all_tiles + splits - 1) / splits, splits > 1 ? MIN_RUN : 1);
+    const int tile_begin = blockIdx.z * run;
+    const int tiles = min(all_tiles, tile_begin + run);
+    if (tile_begin < tiles) load_tile(tile_begin, 0);
     cp_async_commit();
     // the token's queries: rows beyond the heads of this group are zeros
     for (int i = tid; i < ROWS * chunks; i += THREADS) {
@@ -110,8 +118,8 @@ latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__
     for (int j = 0; j < MAX_TILES_A_WARP; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
     const float scale2 = scale * LOG2E;
-    for (int tile = 0; tile < tiles; ++tile) {
-        const int stage = tile & 1;
+    for (int tile = tile_begin; tile < tiles; ++tile) {
+        const int stage = (tile - tile_begin) & 1;
         if (tile + 1 < tiles) load_tile(tile + 1, stage ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
@@ -212,6 +220,26 @@ latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__
         __syncthreads();                                        // the tile, the scores and P are free again
     }
 
+    if (splits > 1) {
+        __syncthreads();                                        // a block without tiles still owes its (empty) piece
+        const size_t piece = ((size_t)t * gridDim.y + blockIdx.y) * splits + blockIdx.z;
+        const int cols = 4 * tiles_a_warp * 8;                  // columns a piece holds (those of all four warps)
+        float* o = part_o + piece * ROWS * cols;
+#pragma unroll
+        for (int j = 0; j < MAX_TILES_A_WARP; ++j) {
+            const int n_tile = first_tile + j;
+            if (j < tiles_a_warp) {
+                const int col = n_tile * 8 + 2 * tq;
+                *reinterpret_cast<float2*>(o + g * cols + col) = make_float2(acc[j][0], acc[j][1]);
+                *reinterpret_cast<float2*>(o + (g + 8) * cols + col) = make_float2(acc[j][2], acc[j][3]);
+            }
+        }
+        if (tid < ROWS) {
+            part_ml[(piece * ROWS + tid) * 2] = row_max[tid];
+            part_ml[(piece * ROWS + tid) * 2 + 1] = row_sum[tid];
+        }
+        return;
+    }
     // ---- out = O / l
     const float inv_lo = 1.f / row_sum[g], inv_hi = 1.f / row_sum[g + 8];
 #pragma unroll
@@ -229,6 +257,32 @@ latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__
     }
 }
 
+// The pieces of a (token, head group) added up: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),
+// in the order of s.  grid: (tokens, head groups); a piece without tiles has m = -inf and counts nothing.
+__global__ void latent_wide_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         bf16* __restrict__ out, const int* __restrict__ positions, int heads,
+                                         int width, int cols, int splits) {
+    const int t = blockIdx.x, head0 = blockIdx.y * ROWS;
+    if (positions[t] < 0) return;                               // the attention kernel wrote zeros
+    const int rows_here = min(ROWS, heads - head0);
+    const size_t first = ((size_t)t * gridDim.y + blockIdx.y) * splits;
+    const int out_cols = min(cols, width);
+    for (int i = threadIdx.x; i < rows_here * out_cols; i += blockDim.x) {
+        const int r = i / out_cols, c = i - r * out_cols;
+        float m = -INFINITY;
+        for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((first + s) * ROWS + r) * 2]);
+        float total = 0.f, value = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[((first + s) * ROWS + r) * 2];
+            if (ms == -INFINITY) continue;
+            const float w = exp2f(ms - m);
+            total += part_ml[((first + s) * ROWS + r) * 2 + 1] * w;
+            value += part_o[((first + s) * ROWS + r) * (size_t)cols + c] * w;
+        }
+        out[((size_t)t * heads + head0 + r) * width + c] = __float2bfloat16_rn(value / total);
+    }
+}
+
 size_t latent_wide_smem(int width) {
     const size_t ld = width + 8;
     return (ROWS + 2 * TILE_KEYS) * ld * sizeof(bf16) + ROWS * (TILE_KEYS + 1) * sizeof(float) +
@@ -243,13 +297,25 @@ MRUN_API int mrun_latent_attention_wide_ok(int width, int value_cols) {
            value_cols <= 4 * MAX_TILES_A_WARP * 8 && latent_wide_smem(width) <= 200 * 1024;
 }
 
+// Columns a piece of a split launch holds for each of its 16 rows.
+MRUN_API int mrun_latent_attention_wide_piece_cols(int value_cols) {
+    int tiles_a_warp = ((value_cols + 7) / 8 + 3) / 4;
+    tiles_a_warp += tiles_a_warp & 1;
+    return 4 * tiles_a_warp * 8;
+}
+
 // q: row t starts at q + t * q_stride, heads contiguous [heads, width].  out: dense [tokens, heads * width];
 // the first value_cols features of every head are written (rounded up to whole pairs of 8).
-// cache: [pages, 1, page_size, width].  positions[t] < 0 = padding.
+// cache: [pages, 1, page_size, width].  positions[t] < 0 = padding.  splits > 1 (few tokens, long
+// contexts): every token's keys are dealt to that many blocks; part_o holds
+// [tokens, head groups, splits, 16, piece_cols] floats and part_ml [.., 16, 2].
 MRUN_API int mrun_latent_attention_wide(const void* q, long q_stride, void* out, const void* cache,
                                         const int* block_tables, int max_blocks, const int* token_slot,
                                         const int* positions, int tokens, int heads, int width, int value_cols,
-                                        int page_size, long cache_rows, float scale, cudaStream_t stream) {
+                                        int page_size, long cache_rows, float scale, int splits, float* part_o,
+                                        float* part_ml, cudaStream_t stream) {
+    MRUN_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+                 "latent_attention_wide: splits=%d needs scratch for the pieces", splits);
     MRUN_REQUIRE(tokens >= 0 && heads > 0 && page_size > 0 && max_blocks > 0, "latent_attention_wide: bad sizes");
     MRUN_REQUIRE(mrun_latent_attention_wide_ok(width, value_cols),
                  "latent_attention_wide: rows of %d features with %d value columns are not supported", width, value_cols);
@@ -261,10 +327,16 @@ MRUN_API int mrun_latent_attention_wide(const void* q, long q_stride, void* out,
     const size_t smem = latent_wide_smem(width);
     MRUN_CHECK_CUDA(cudaFuncSetAttribute(latent_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                     "latent_attention_wide");
-    const dim3 grid(tokens, (heads + ROWS - 1) / ROWS);
+    const dim3 grid(tokens, (heads + ROWS - 1) / ROWS, splits);
     latent_wide_kernel<<<grid, THREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)cache,
                                                         block_tables, max_blocks, token_slot, positions, heads, width,
-                                                        value_cols, page_size, page_shift_of(page_size), scale);
+                                                        value_cols, page_size, page_shift_of(page_size), scale, splits,
+                                                        part_o, part_ml);
     MRUN_CHECK_LAUNCH("latent_attention_wide");
+    if (splits > 1) {
+        latent_wide_merge_kernel<<<dim3(grid.x, grid.y), 256, 0, stream>>>(
+            part_o, part_ml, (bf16*)out, positions, heads, width, mrun_latent_attention_wide_piece_cols(value_cols), splits);
+        MRUN_CHECK_LAUNCH("latent_attention_wide (merge)");
+    }
     return 0;
 }

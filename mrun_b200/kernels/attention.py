@@ -210,6 +210,9 @@ def decode_fuses_input(ctx, dtype: torch.dtype, heads: int, kv_heads: int, head_
     return ctx.all_decode and ratio <= 16 and supports_tensor_cores(dtype, head_dim, ratio)
 
 
+LATENT_WIDE_MAX_SPLITS = 32     # the most blocks one token's keys are dealt to by the kernel for wide latent rows
+
+
 def latent_wide_ok(dtype: torch.dtype, width: int, value_dim: int) -> bool:
     """Whether the tensor-core kernel for wide latent rows takes this shape (bfloat16, rows of a
     multiple of 16 features, at most 512 value columns)."""
@@ -230,10 +233,21 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     if (value_dim and cache.v is cache.k and kv_heads == 1 and window == 0 and raw is None
             and not supports_tensor_cores(q.dtype, head_dim, ratio) and latent_wide_ok(q.dtype, head_dim, value_dim)):
         ops._check(q, "q", torch.bfloat16, dense=False); ops._check(out, "out", torch.bfloat16)
+        # few tokens and long contexts: every token's keys are dealt to several blocks, so that the
+        # step's blocks fill the device about twice (a function of the step's shape only)
+        groups = -(-heads // 16)
+        blocks = ctx.num_tokens * groups
+        splits = max(1, min(LATENT_WIDE_MAX_SPLITS, 2 * ops.sm_count(q.device) // blocks, -(-ctx.max_kv_len // 128)))
+        part_o = part_ml = None
+        if splits > 1:
+            cols = int(_lib.core()._dll.mrun_latent_attention_wide_piece_cols(_c_int(value_dim)))
+            part_o = torch.empty((blocks * splits, 16, cols), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((blocks * splits, 16, 2), dtype=torch.float32, device=q.device)
         _lib.core().call("mrun_latent_attention_wide", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(cache.k),
                          _ptr(group.block_tables), _c_int(group.max_blocks), _ptr(ctx.token_slot), _ptr(ctx.positions),
                          _c_int(ctx.num_tokens), _c_int(heads), _c_int(head_dim), _c_int(value_dim), _c_int(page_size),
-                         _c_long(pages * page_size), _c_float(scale), _stream())
+                         _c_long(pages * page_size), _c_float(scale), _c_int(splits), _ptr(part_o), _ptr(part_ml),
+                         _stream())
         return out
     if not supports_tensor_cores(q.dtype, head_dim, ratio):
         return ops.paged_attention_generic(q, q_stride, out, cache.k, cache.v, group.block_tables,
