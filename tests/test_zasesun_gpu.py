@@ -146,6 +146,15 @@ def test_relu2_soft_cap_and_per_head_products(dtype):
         assert bool((rows_out[:, :, n:] == 7.0).all())
 
 
+def test_which_rows_the_wide_kernel_takes():
+    from mrun_b200.kernels.attention import latent_wide_ok, supports_tensor_cores
+    assert latent_wide_ok(torch.bfloat16, 576, 512) and latent_wide_ok(torch.bfloat16, 272, 264)
+    assert not latent_wide_ok(torch.float32, 576, 512)          # the 32-bit path stays on CUDA cores
+    assert not latent_wide_ok(torch.bfloat16, 1024, 600)        # more value columns than four warps hold
+    assert not latent_wide_ok(torch.bfloat16, 568, 512)         # rows are padded to multiples of 16
+    assert not supports_tensor_cores(torch.bfloat16, 272, 20)   # such rows are beyond the per-head-size kernels
+
+
 # ------------------------------------------------------------------ parts alone
 
 def random_part_tensors(specs, seed, std=0.15):
