@@ -257,29 +257,50 @@ latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__
     }
 }
 
-// The pieces of a (token, head group) added up: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),
-// in the order of s.  grid: (tokens, head groups); a piece without tiles has m = -inf and counts nothing.
-__global__ void latent_wide_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         bf16* __restrict__ out, const int* __restrict__ positions, int heads,
-                                         int width, int cols, int splits) {
-    const int t = blockIdx.x, head0 = blockIdx.y * ROWS;
+// The pieces of a (token, head) added up: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), in the
+// order of s.  grid: (tokens, heads); a block's threads share the row's weights and walk its columns.
+// A piece without tiles has m = -inf and counts nothing.
+constexpr int MAX_SPLITS = 64;
+
+__global__ void __launch_bounds__(128)
+latent_wide_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         bf16* __restrict__ out, const int* __restrict__ positions, int heads, int width,
+                         int cols, int splits) {
+    __shared__ float weight[MAX_SPLITS];
+    __shared__ float inv_total;
+    const int t = blockIdx.x, head = blockIdx.y;
     if (positions[t] < 0) return;                               // the attention kernel wrote zeros
-    const int rows_here = min(ROWS, heads - head0);
-    const size_t first = ((size_t)t * gridDim.y + blockIdx.y) * splits;
-    const int out_cols = min(cols, width);
-    for (int i = threadIdx.x; i < rows_here * out_cols; i += blockDim.x) {
-        const int r = i / out_cols, c = i - r * out_cols;
+    const int groups = (heads + ROWS - 1) / ROWS;
+    const size_t first = ((size_t)t * groups + head / ROWS) * splits;
+    const int r = head % ROWS;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
         float m = -INFINITY;
-        for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((first + s) * ROWS + r) * 2]);
-        float total = 0.f, value = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[((first + s) * ROWS + r) * 2];
-            if (ms == -INFINITY) continue;
-            const float w = exp2f(ms - m);
-            total += part_ml[((first + s) * ROWS + r) * 2 + 1] * w;
-            value += part_o[((first + s) * ROWS + r) * (size_t)cols + c] * w;
+        for (int s = lane; s < splits; s += 32) m = fmaxf(m, part_ml[((first + s) * ROWS + r) * 2]);
+        m = warp_max(m);
+        float total = 0.f;
+        for (int s0 = 0; s0 < splits; s0 += 32) {               // the totals are added in the order of s
+            const int s = s0 + lane;
+            float w = 0.f, l = 0.f;
+            if (s < splits) {
+                const float ms = part_ml[((first + s) * ROWS + r) * 2];
+                w = ms == -INFINITY ? 0.f : exp2f(ms - m);
+                l = part_ml[((first + s) * ROWS + r) * 2 + 1] * w;
+                weight[s] = w;
+            }
+            for (int i = 0; i < 32; ++i) total += __shfl_sync(0xffffffffu, l, i);
         }
-        out[((size_t)t * heads + head0 + r) * width + c] = __float2bfloat16_rn(value / total);
+        if (lane == 0) inv_total = 1.f / total;
+    }
+    __syncthreads();
+    const int out_cols = min(cols, width);
+    for (int c = threadIdx.x; c < out_cols; c += blockDim.x) {
+        float value = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float w = weight[s];
+            if (w != 0.f) value += part_o[((first + s) * ROWS + r) * (size_t)cols + c] * w;
+        }
+        out[((size_t)t * heads + head) * width + c] = __float2bfloat16_rn(value * inv_total);
     }
 }
 
@@ -314,7 +335,7 @@ MRUN_API int mrun_latent_attention_wide(const void* q, long q_stride, void* out,
                                         const int* positions, int tokens, int heads, int width, int value_cols,
                                         int page_size, long cache_rows, float scale, int splits, float* part_o,
                                         float* part_ml, cudaStream_t stream) {
-    MRUN_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+    MRUN_REQUIRE(splits >= 1 && splits <= MAX_SPLITS && heads <= 65535 && (splits == 1 || (part_o != nullptr && part_ml != nullptr)),
                  "latent_attention_wide: splits=%d needs scratch for the pieces", splits);
     MRUN_REQUIRE(tokens >= 0 && heads > 0 && page_size > 0 && max_blocks > 0, "latent_attention_wide: bad sizes");
     MRUN_REQUIRE(mrun_latent_attention_wide_ok(width, value_cols),
@@ -334,7 +355,7 @@ MRUN_API int mrun_latent_attention_wide(const void* q, long q_stride, void* out,
                                                         part_o, part_ml);
     MRUN_CHECK_LAUNCH("latent_attention_wide");
     if (splits > 1) {
-        latent_wide_merge_kernel<<<dim3(grid.x, grid.y), 256, 0, stream>>>(
+        latent_wide_merge_kernel<<<dim3(tokens, heads), 128, 0, stream>>>(
             part_o, part_ml, (bf16*)out, positions, heads, width, mrun_latent_attention_wide_piece_cols(value_cols), splits);
         MRUN_CHECK_LAUNCH("latent_attention_wide (merge)");
     }
