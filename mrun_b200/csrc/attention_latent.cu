@@ -75,16 +75,18 @@ latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__
     const int chunks = width >> 3;
     Paging pg{block_tables + (size_t)token_slot[t] * max_blocks, 1, 0, page_size, page_shift};
 
+    // a warp takes every fourth key of the tile: one look at the block table a key, then the
+    // row's 16-byte chunks lane by lane
     auto load_tile = [&](int tile, int stage) {
         bf16* dst = k_ring + (size_t)stage * TILE_KEYS * ld;
-        for (int i = tid; i < TILE_KEYS * chunks; i += THREADS) {
-            const int key_in = i / chunks, c = i - key_in * chunks;
+        for (int key_in = warp; key_in < TILE_KEYS; key_in += THREADS / 32) {
             const int key = tile * TILE_KEYS + key_in;
             bool valid = key <= pos;
             // cache_row's template argument is a compile-time head size; the width is a run-time
             // value here, so the row number is asked for with size 1 and scaled
             const long row = cache_row<1>(pg, key, valid);
-            cp_async_16(dst + key_in * ld + c * 8, cache + (valid ? row * width : 0) + c * 8, valid);
+            const bf16* src = cache + (valid ? row * width : 0);
+            for (int c = lane; c < chunks; c += 32) cp_async_16(dst + key_in * ld + c * 8, src + c * 8, valid);
         }
     };
 
@@ -128,25 +130,35 @@ latent_wide_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__
 
         // ---- S = Q K^T: this warp's eight keys
         {
-            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            // four sums side by side (one a 16-feature step of each 64), so that a product does not
+            // wait for the one before it; they are added in a fixed order at the end
+            float s[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f},
+                  s3[4] = {0.f, 0.f, 0.f, 0.f};
             const bf16* a_ptr = q_tile + (lane & 15) * ld + (lane >> 4) * 8;
             const bf16* b_ptr = k_tile + (warp * 8 + (lane & 7)) * ld + (lane >> 3) * 8;
-            for (int k0 = 0; k0 + 32 <= width; k0 += 32) {
-                unsigned a0[4], a1[4], b[4];
+            int k0 = 0;
+            for (; k0 + 64 <= width; k0 += 64) {
+                unsigned a0[4], a1[4], a2[4], a3[4], b0[4], b1[4];
                 ldmatrix_x4(a0, a_ptr + k0);
                 ldmatrix_x4(a1, a_ptr + k0 + 16);
-                ldmatrix_x4(b, b_ptr + k0);
-                mma_bf16(s, a0, b[0], b[1]);
-                mma_bf16(s, a1, b[2], b[3]);
+                ldmatrix_x4(a2, a_ptr + k0 + 32);
+                ldmatrix_x4(a3, a_ptr + k0 + 48);
+                ldmatrix_x4(b0, b_ptr + k0);
+                ldmatrix_x4(b1, b_ptr + k0 + 32);
+                mma_bf16(s, a0, b0[0], b0[1]);
+                mma_bf16(s1, a1, b0[2], b0[3]);
+                mma_bf16(s2, a2, b1[0], b1[1]);
+                mma_bf16(s3, a3, b1[2], b1[3]);
             }
-            if (width & 16) {                                   // a last half step of 16 features
-                const int k0 = width - 16;
+            for (; k0 < width; k0 += 16) {                      // the last 16, 32 or 48 features
                 unsigned a0[4], b[4];
                 ldmatrix_x4(a0, a_ptr + k0);
-                // lanes 16..31 would address features past the row: they repeat the first half
+                // lanes 16..31 would address features past the step: they repeat the first half
                 ldmatrix_x4(b, k_tile + (warp * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8 + k0);
                 mma_bf16(s, a0, b[0], b[1]);
             }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] = (s[i] + s1[i]) + (s2[i] + s3[i]);
             const int key0 = tile * TILE_KEYS + warp * 8 + 2 * tq;
             float* s_row = scores + g * (TILE_KEYS + 1) + warp * 8 + 2 * tq;
             s_row[0] = key0 <= pos ? s[0] * scale2 : -INFINITY;
