@@ -25,7 +25,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 
 from . import native
-from .needs import FixedState, PagedKV, PagedLatent
+from .needs import FixedState, PagedKV, PagedLatent, PagedMaps, split_need
 from .pages import OutOfPages
 
 FREED = -1  # block-table entry of a logical block whose page was given back (or never taken)
@@ -112,11 +112,14 @@ class PagedGroup:
 class EntryCache:
     """The cache of one schedule entry, as its mixer sees it."""
 
-    def __init__(self, need, group_key, writable: bool, k=None, v=None, state=None):
+    def __init__(self, need, group_key, writable: bool, k=None, v=None, state=None, states=None):
         self.need = need
         self.group_key = group_key
         self.writable = writable
         self.k, self.v, self.state = k, v, state
+        # every fixed-size state of the entry by its name ([max_requests, *shape] each); ``state``
+        # is the first of them
+        self.states = dict(states or {})
 
 
 def token_bytes(needs: Sequence[object], shares: Sequence[Optional[int]], element_size: int) -> Tuple[int, int]:
@@ -127,15 +130,19 @@ def token_bytes(needs: Sequence[object], shares: Sequence[Optional[int]], elemen
     for need, share in zip(needs, shares):
         if share is not None or need is None:
             continue
-        if isinstance(need, PagedKV):
-            per_token += 2 * need.kv_heads * need.head_dim * element_size
-        elif isinstance(need, PagedLatent):
-            per_token += need.width * element_size
-        elif isinstance(need, FixedState):
+        paged, states = split_need(need)
+        if isinstance(paged, PagedKV):
+            per_token += 2 * paged.kv_heads * paged.head_dim * element_size
+        elif isinstance(paged, PagedLatent):
+            per_token += paged.width * element_size
+        elif isinstance(paged, PagedMaps):
+            per_token += paged.kv_heads * (paged.maps * paged.key_dim
+                                           + paged.value_chunks * paged.value_chunk_dim) * element_size
+        for state in states:
             count = 1
-            for extent in need.shape:
+            for extent in state.shape:
                 count *= extent
-            per_slot += count * _STATE_BYTES.get(need.dtype, 4)
+            per_slot += count * _STATE_BYTES.get(state.dtype, 4)
     return per_token, per_slot
 
 
@@ -169,42 +176,51 @@ class CacheManager:
                 owner = self.entries[share]
                 if owner is None:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {share}, which keeps none")
-                self.entries.append(EntryCache(owner.need, owner.group_key, False, owner.k, owner.v, owner.state))
+                self.entries.append(EntryCache(owner.need, owner.group_key, False, owner.k, owner.v, owner.state,
+                                               owner.states))
                 continue
-            if need is None:
+            paged, fixed = split_need(need)
+            if paged is None and not fixed:
                 self.entries.append(None)
-            elif isinstance(need, (PagedKV, PagedLatent)):
-                if need.window is not None and need.window < 1:
-                    raise ValueError(f"schedule entry {i}: window must be at least 1, got {need.window}")
-                key = need.group_key()
-                group = self.groups.get(key)
-                if group is None:
-                    group = self.groups[key] = PagedGroup(key, need.window, self.max_blocks)
-                    if device is not None:
-                        import torch
-                        group.table_device = torch.full((max_requests, self.max_blocks), FREED,
-                                                        dtype=torch.int32, device=device)
-                group.entries.append(i)
-                k = v = None
+                continue
+            states = {}
+            for item in fixed:
+                tensor = None
                 if device is not None:
                     import torch
-                    if isinstance(need, PagedLatent):       # one row a token: the key and the value
-                        k = v = torch.zeros((num_pages, 1, page_size, need.width), dtype=dtype, device=device)
-                    else:
-                        shape = (num_pages, need.kv_heads, page_size, need.head_dim)
-                        k = torch.zeros(shape, dtype=dtype, device=device)
-                        v = torch.zeros(shape, dtype=dtype, device=device)
-                self.entries.append(EntryCache(need, key, True, k=k, v=v))
-            elif isinstance(need, FixedState):
-                state = None
+                    tensor = torch.zeros((max_requests, *item.shape), dtype=getattr(torch, item.dtype), device=device)
+                    self._state_tensors.append(tensor)
+                states[item.name] = tensor
+            first_state = next(iter(states.values()), None)
+            if paged is None:
+                self.entries.append(EntryCache(need, fixed[0].group_key(), True, state=first_state, states=states))
+                continue
+            if paged.window is not None and paged.window < 1:
+                raise ValueError(f"schedule entry {i}: window must be at least 1, got {paged.window}")
+            key = paged.group_key()
+            group = self.groups.get(key)
+            if group is None:
+                group = self.groups[key] = PagedGroup(key, paged.window, self.max_blocks)
                 if device is not None:
                     import torch
-                    state = torch.zeros((max_requests, *need.shape), dtype=getattr(torch, need.dtype),
-                                        device=device)
-                    self._state_tensors.append(state)
-                self.entries.append(EntryCache(need, need.group_key(), True, state=state))
-            else:
-                raise TypeError(f"schedule entry {i}: unknown cache need {need!r}")
+                    group.table_device = torch.full((max_requests, self.max_blocks), FREED,
+                                                    dtype=torch.int32, device=device)
+            group.entries.append(i)
+            k = v = None
+            if device is not None:
+                import torch
+                if isinstance(paged, PagedLatent):       # one row a token: the key and the value
+                    k = v = torch.zeros((num_pages, 1, page_size, paged.width), dtype=dtype, device=device)
+                elif isinstance(paged, PagedMaps):
+                    k = torch.zeros((paged.maps, num_pages, paged.kv_heads, page_size, paged.key_dim),
+                                    dtype=dtype, device=device)
+                    v = torch.zeros((paged.value_chunks, num_pages, paged.kv_heads, page_size,
+                                     paged.value_chunk_dim), dtype=dtype, device=device)
+                else:
+                    shape = (num_pages, paged.kv_heads, page_size, paged.head_dim)
+                    k = torch.zeros(shape, dtype=dtype, device=device)
+                    v = torch.zeros(shape, dtype=dtype, device=device)
+            self.entries.append(EntryCache(paged, key, True, k=k, v=v, state=first_state, states=states))
 
         # the books: pools, block tables, lengths, plans (csrc/host/cache_core.cpp)
         self._lib = native.library()
@@ -251,7 +267,11 @@ class CacheManager:
     def bytes_per_page(self) -> int:
         total = 0
         for entry in self.entries:
-            if entry is not None and entry.writable and isinstance(entry.need, (PagedKV, PagedLatent)) and entry.k is not None:
+            if entry is None or not entry.writable or entry.k is None:
+                continue
+            if isinstance(entry.need, PagedMaps):
+                total += (entry.k[:, 0].numel() + entry.v[:, 0].numel()) * entry.k.element_size()
+            elif isinstance(entry.need, (PagedKV, PagedLatent)):
                 total += (1 if entry.v is entry.k else 2) * entry.k[0].numel() * entry.k.element_size()
         return total
 
@@ -292,7 +312,7 @@ class CacheManager:
         a mixer that keeps such state cannot be cut back."""
         if request.released:
             raise ValueError(f"request {request.request_id!r} is released")
-        if length != request.length and any(e is not None and isinstance(e.need, FixedState) for e in self.entries):
+        if length != request.length and any(e is not None and e.states for e in self.entries):
             raise ValueError("a request with per-request state of fixed size cannot be cut back")
         if self._lib.mrun_cache_trim(self._core, request.slot, int(length)):
             raise ValueError(f"request {request.request_id!r}: {self._message()}")

@@ -39,11 +39,52 @@ class PagedLatent:
 
 
 @dataclass(frozen=True)
+class PagedMaps:
+    """Keys of ``maps`` attention maps and values cut into ``value_chunks`` chunks a token and kv
+    head: key pages [maps, pages, kv_heads, page_size, key_dim] and value pages [value_chunks,
+    pages, kv_heads, page_size, value_chunk_dim], so that every map and every chunk is a page
+    tensor of the :class:`PagedKV` shape.  Shares the pages' books with :class:`PagedKV` of the
+    same window."""
+
+    maps: int
+    kv_heads: int
+    key_dim: int
+    value_chunks: int
+    value_chunk_dim: int
+    window: Optional[int] = None
+
+    def group_key(self) -> tuple:
+        return ("paged", self.window)
+
+
+@dataclass(frozen=True)
 class FixedState:
-    """Per-request state of a fixed shape, zero when a request starts."""
+    """Per-request state of a fixed shape, zero when a request starts.  A part that keeps several
+    states gives each a ``name`` and declares them together (see :func:`split_need`)."""
 
     shape: Tuple[int, ...]
     dtype: str = "float32"
+    name: str = "state"
 
     def group_key(self) -> tuple:
         return ("state",)
+
+
+PAGED = (PagedKV, PagedLatent, PagedMaps)
+
+
+def split_need(need):
+    """A part's need may be one need, None, or a tuple of at most one paged need and any number
+    of :class:`FixedState` with different names: returns (paged need or None, the states)."""
+    if need is None:
+        return None, ()
+    items = tuple(need) if isinstance(need, (tuple, list)) else (need,)
+    paged = [n for n in items if isinstance(n, PAGED)]
+    states = tuple(n for n in items if isinstance(n, FixedState))
+    if len(paged) > 1:
+        raise TypeError("a schedule entry may have one paged cache need")
+    if len(paged) + len(states) != len(items):
+        raise TypeError(f"unknown cache need among {items!r}")
+    if len({s.name for s in states}) != len(states):
+        raise TypeError("the states of a schedule entry need different names")
+    return (paged[0] if paged else None), states

@@ -45,6 +45,8 @@ class RMSNormSpec:
     size: int
     eps: float
     bare: bool = False
+    # the checkpoint holds one number for all coordinates (a tensor without dimensions)
+    scalar: bool = False
 
 
 # --------------------------------------------------------------------------- position encodings
@@ -123,6 +125,68 @@ class LatentAttentionSpec:
     position: Optional[Any] = None
 
 
+@dataclass(frozen=True)
+class DifferentialAttentionSpec:
+    """Softmax attention with two maps a head: the query has ``heads * 2 * dim`` rows and the key
+    ``kv_heads * 2 * dim``, head by head as [map 1, map 2]; both maps weigh the same values
+    (``vdim`` a kv head).  With a1, a2 the maps' outputs and lambda = exp(lq1 . lk1) - exp(lq2 .
+    lk2) + ``diff`` (one number a layer, from four vectors of ``dim`` entries): o = a1 - lambda *
+    a2, divided by its root mean square over the head's ``vdim`` values (``eps`` inside the
+    root, no weight) and multiplied by 1 - ``diff``.  ``position`` rotates the first features of
+    every map of every q and k head."""
+
+    kind: ClassVar[str] = "differential_attention"
+    hidden: int
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    softmax_scale: float
+    diff: float
+    eps: float
+    position: Optional[Any] = None
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class DecayAttentionSpec:
+    """Linear attention with one decay a head and a state of fixed size: q, k (``heads`` x
+    ``dim``) and v (``heads`` x ``vdim``) pass SiLU; S_t = decay_h * S_(t-1) + k_t v_t^T, o_t =
+    S_t^T q_t.  The heads' outputs together are RMS-normed with a weight, multiplied by the
+    sigmoid of a gate projection and projected out."""
+
+    kind: ClassVar[str] = "decay_attention"
+    hidden: int
+    heads: int
+    dim: int
+    vdim: int
+    decay: Tuple[float, ...]
+    eps: float
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec:
+    """Gated delta rule with a decay per head and key channel.  q, k (``kv_heads`` x ``dim``) and
+    v (``heads`` x ``vdim``) pass a causal convolution of ``conv`` taps per channel and SiLU; q
+    and k become unit vectors per head (1e-6 inside the root), q times dim^-1/2.  beta =
+    sigmoid(b x); g = exp(-exp(A_log_h) * softplus(a2 (a1 x) + dt_bias)) per head and key
+    channel.  Per head: S <- g * S (rows); u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  Each
+    head's o is RMS-normed over ``vdim`` with a weight shared by the heads and multiplied by
+    sigmoid(g2 (g1 x)).  ``decay_rank`` and ``gate_rank`` are the inner sizes of the two
+    low-rank projections."""
+
+    kind: ClassVar[str] = "channel_delta"
+    hidden: int
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: int
+    gate_rank: int
+    eps: float
+
+
 # --------------------------------------------------------------------------- feed-forwards
 
 @dataclass(frozen=True)
@@ -157,6 +221,23 @@ class RoutedMLPSpec:
     renormalize: bool = False
 
 
+@dataclass(frozen=True)
+class TableRoutedMLPSpec:
+    """A mixture of ``experts`` gated feed-forwards without a router: row ``token id`` of an
+    integer table [``vocab``, ``top``] names the token's experts, each weighing 1 / ``top``.
+    Expert: g = min(gate x, limit), u = clamp(up x, -limit, limit), y = g * sigmoid(alpha * g) *
+    (u + 1), output down y."""
+
+    kind: ClassVar[str] = "table_routed_mlp"
+    hidden: int
+    vocab: int
+    experts: int
+    top: int
+    expert_ff: int
+    limit: float
+    alpha: float = 1.702
+
+
 # --------------------------------------------------------------------------- transforms
 
 @dataclass(frozen=True)
@@ -165,6 +246,14 @@ class SoftCapSpec:
 
     kind: ClassVar[str] = "soft_cap"
     cap: float
+
+
+@dataclass(frozen=True)
+class ScaleSpec:
+    """x -> factor * x."""
+
+    kind: ClassVar[str] = "scale"
+    factor: float
 
 
 # --------------------------------------------------------------------------- layers and model
@@ -191,6 +280,16 @@ class LayerSpec:
     mixer_post_norm_prefix: str = "post_mixer_norm"
     feed_forward_post_norm_prefix: str = "post_feed_forward_norm"
     residual_scale: float = 1.0
+    # the ``streams`` arrangement: how many residual streams a token has (0: the layer's
+    # checkpoint has no stream coefficients and the streams reduce to the plain residual sum),
+    # the prefixes of the two sublayers' coefficients (``.in`` [S], ``.out`` [S], ``.mix`` [S, S]
+    # indexed [from, to]), and the taps of the causal convolution whose output is added to the
+    # mixer's input (0: none; its weight is ``<prefix>.<input_conv_name>`` [hidden, taps])
+    streams: int = 0
+    mixer_streams_prefix: str = "hc1"
+    feed_forward_streams_prefix: str = "hc2"
+    input_conv_taps: int = 0
+    input_conv_name: str = "canon1"
 
 
 @dataclass(frozen=True)
@@ -221,6 +320,8 @@ class ModelSpec:
     # the float32 logits of the wanted rows
     embedding_transform: Any = None
     logits_transform: Any = None
+    # residual streams a token (layers of the ``streams`` arrangement); 1: the plain residual row
+    streams: int = 1
     # tensors that may be present in a checkpoint and are dropped unread: the vision tower, heads
     # for multi-token prediction and rotary frequency tables
     # (crates/mrun-engine/src/load.rs:168-173, crates/mrun-engine/src/models/qwen3.rs:107)

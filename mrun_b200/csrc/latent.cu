@@ -9,6 +9,7 @@
 //   route_top_k       router logits -> a dense row of expert weights (zero where not chosen)
 //   relu2_scaled      relu(u)^2 times the expert weight of the column's expert
 //   soft_cap          cap * tanh(x / cap) in place
+//   scale             x * factor in place
 #include "common.cuh"
 
 using namespace mrun;
@@ -323,6 +324,11 @@ __global__ void soft_cap_kernel(float* __restrict__ x, long total, float cap) {
     if (i < total) x[i] = cap * tanhf(x[i] / cap);
 }
 
+__global__ void scale_kernel(float* __restrict__ x, long total, float factor) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] *= factor;
+}
+
 }  // namespace
 
 MRUN_API int mrun_latent_prepare(const void* down, int act_dtype, long ld, const float* q_weight,
@@ -456,6 +462,14 @@ MRUN_API int mrun_relu2_scaled(const void* u, void* act, int act_dtype, const fl
     else
         return mrun_set_error("relu2_scaled: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("relu2_scaled");
+    return 0;
+}
+
+MRUN_API int mrun_scale_f32(float* x, long total, float factor, cudaStream_t stream) {
+    MRUN_REQUIRE(total >= 0, "scale: bad size %ld", total);
+    if (total == 0) return 0;
+    scale_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, total, factor);
+    MRUN_CHECK_LAUNCH("scale");
     return 0;
 }
 

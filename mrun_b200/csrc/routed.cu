@@ -8,6 +8,14 @@
 //   relu2_rows    relu(u)^2 times the row's weight
 //   combine_rows  out[t] = base[t] + the rows of token t's pairs, added in the order they were chosen
 //
+// And two kernels for experts that are chosen by a table instead of a router and have a gate:
+//
+//   table_route   a token's experts are row token_id of an integer table [vocab, top]; each
+//                 weighs 1 / top (the dense weight row and the chosen list, as route_top_k gives them)
+//   clamped_glu   a block of columns [gate (ff) | up (ff)] per expert: g = min(gate, limit),
+//                 u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1), times the
+//                 token's weight of the block's expert or the row's weight
+//
 // Inside an expert's range the rows stand in the order in which the pairs arrived (an atomic
 // counter); a row's result does not depend on where in the range it stands, and the combine adds
 // a token's rows in a fixed order, so the output has the same bits every run.
@@ -122,7 +130,73 @@ __global__ void combine_rows_kernel(const TB* __restrict__ base, const TA* __res
     }
 }
 
+// A warp a token.
+__global__ void table_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, float* __restrict__ weights,
+                                   int* __restrict__ chosen, int tokens, int vocab, int experts, int top) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    for (int e = lane; e < experts; e += 32) weights[(size_t)t * experts + e] = 0.f;
+    __syncwarp();
+    const float share = 1.f / (float)top;
+    for (int j = lane; j < top; j += 32) {
+        const int e = ok ? table[(size_t)id * top + j] : -1;
+        if (chosen) chosen[(size_t)t * top + j] = (e >= 0 && e < experts) ? e : 0;
+        if (e >= 0 && e < experts) weights[(size_t)t * experts + e] = share;
+    }
+}
+
+// u: [rows, blocks * 2 * ff]; act: [rows, blocks * ff].  weights: per (row, block) when
+// per_block, else one per row, or null.
+template <typename TA, bool EXACT>
+__global__ void clamped_glu_kernel(const TA* __restrict__ u, TA* __restrict__ act, const float* __restrict__ weights,
+                                   int per_block, long total, int blocks, int ff, float limit, float alpha) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long row = i / ((long)blocks * ff);
+    const int c = (int)(i - row * blocks * ff);
+    const int e = c / ff, j = c - e * ff;
+    const TA* base = u + (row * blocks + e) * 2 * ff;
+    const float g = fminf(to_float(base[j]), limit);
+    const float up = fminf(fmaxf(to_float(base[ff + j]), -limit), limit);
+    const float w = weights ? (per_block ? weights[row * blocks + e] : weights[row]) : 1.f;
+    float s;
+    if constexpr (EXACT) s = 1.f / (1.f + expf(-alpha * g));
+    else s = __fdividef(1.f, 1.f + __expf(-alpha * g));
+    act[i] = from_float<TA>(g * s * (up + 1.f) * w);
+}
+
 }  // namespace
+
+MRUN_API int mrun_table_route(const int* ids, const int* table, float* weights, int* chosen, int tokens, int vocab,
+                              int experts, int top, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && vocab > 0 && experts > 0 && top > 0 && top <= experts,
+                 "table_route: bad sizes tokens=%d vocab=%d experts=%d top=%d", tokens, vocab, experts, top);
+    if (tokens == 0) return 0;
+    table_route_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(ids, table, weights, chosen, tokens, vocab, experts, top);
+    MRUN_CHECK_LAUNCH("table_route");
+    return 0;
+}
+
+MRUN_API int mrun_clamped_glu(const void* u, void* act, int act_dtype, const float* weights, int per_block, int rows,
+                              int blocks, int ff, float limit, float alpha, cudaStream_t stream) {
+    MRUN_REQUIRE(rows >= 0 && blocks > 0 && ff > 0, "clamped_glu: bad sizes rows=%d blocks=%d ff=%d", rows, blocks, ff);
+    if (rows == 0) return 0;
+    const long total = (long)rows * blocks * ff;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    if (act_dtype == MRUN_F32)
+        clamped_glu_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)u, (float*)act, weights, per_block, total,
+                                                                   blocks, ff, limit, alpha);
+    else if (act_dtype == MRUN_BF16)
+        clamped_glu_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)u, (__nv_bfloat16*)act,
+                                                                            weights, per_block, total, blocks, ff, limit,
+                                                                            alpha);
+    else
+        return mrun_set_error("clamped_glu: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("clamped_glu");
+    return 0;
+}
 
 // counts, ends, cursor: int32 [experts] (counts zeroed by the caller); source, row_weight: [pairs];
 // dest: [pairs] (= [tokens, top]).

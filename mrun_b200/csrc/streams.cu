@@ -1,0 +1,136 @@
+// Several residual streams a token (hyper-connections).
+//
+// A model with S streams keeps [tokens, S, width] 32-bit rows instead of one residual row.  A
+// sublayer reads a weighted sum of the streams and writes back into all of them:
+//
+//     u      = sum_s in[s] * x_s                       (what the sublayer's norm sees)
+//     x_t'   = sum_s mix[s, t] * x_s + out[t] * y      (all streams at once from the old ones)
+//
+// The write of one sublayer and the read of the next are one kernel here: the block of a token
+// loads its S rows once, applies the pending write (if any), stores the new rows, forms the next
+// sublayer's u and norms it.  With S = 1, mix = out = in = 1 this is the plain residual sum
+// followed by an RMS norm.  All sums are 32-bit and run over s in rising order, so a row's bits
+// depend on the row only.
+//
+// Kernels:
+//   embed_streams   the embedding row of a token copied into each of its S streams
+//   streams_step    pending write + read + RMS norm (eps inside the root), see above
+#include "common.cuh"
+
+using namespace mrun;
+
+namespace {
+
+constexpr int MAX_STREAMS = 8;
+
+template <typename TW>
+__global__ void embed_streams_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                                     float* __restrict__ out, int hidden, int vocab, int copies) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const TW* row = table + (size_t)(ok ? id : 0) * hidden;
+    float* dst = out + (size_t)t * copies * hidden;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        const float v = ok ? to_float(row[h]) : 0.f;
+        for (int s = 0; s < copies; ++s) dst[(size_t)s * hidden + h] = v;
+    }
+}
+
+// One block a row.  `rows` (optional) names the tokens to read: the streams are then left as they
+// are and row r of the outputs belongs to token rows[r].  `y` is the pending sublayer output
+// (32-bit, one row a token) or null; `norm_w` null leaves u un-normed (32-bit output `u_out`).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+streams_step_kernel(float* __restrict__ streams, const float* __restrict__ y, const float* __restrict__ mix,
+                    const float* __restrict__ out_c, const float* __restrict__ in_c,
+                    const float* __restrict__ norm_w, float eps, TO* __restrict__ h_out,
+                    float* __restrict__ u_out, const int* __restrict__ rows, int S, int width) {
+    extern __shared__ float u_row[];          // width
+    __shared__ float scratch[33];
+    __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const long t = rows ? rows[r] : r;
+    if (tid < S * S) c_mix[tid] = (y && mix) ? mix[tid] : ((tid / S == tid % S) ? 1.f : 0.f);
+    if (tid < S) { c_out[tid] = (y && out_c) ? out_c[tid] : (y ? 1.f : 0.f); c_in[tid] = in_c ? in_c[tid] : 1.f; }
+    __syncthreads();
+    float* x = streams + t * S * width;
+    float ss = 0.f;
+    for (int c = tid; c < width; c += blockDim.x) {
+        float old[MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s) old[s] = s < S ? x[(size_t)s * width + c] : 0.f;
+        float u = 0.f;
+        if (y) {
+            const float yv = y[t * width + c];
+#pragma unroll
+            for (int to = 0; to < MAX_STREAMS; ++to) {
+                if (to < S) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int s = 0; s < MAX_STREAMS; ++s)
+                        if (s < S) v = fmaf(c_mix[s * S + to], old[s], v);
+                    v = fmaf(c_out[to], yv, v);
+                    if (!rows) x[(size_t)to * width + c] = v;
+                    u = fmaf(c_in[to], v, u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+                if (s < S) u = fmaf(c_in[s], old[s], u);
+        }
+        u_row[c] = u;
+        ss += u * u;
+    }
+    if (u_out)
+        for (int c = tid; c < width; c += blockDim.x) u_out[(size_t)r * width + c] = u_row[c];
+    if (!norm_w) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)width + eps);
+    for (int c = tid; c < width; c += blockDim.x)
+        h_out[(size_t)r * width + c] = from_float<TO>(u_row[c] * inv * norm_w[c]);
+}
+
+}  // namespace
+
+MRUN_API int mrun_embed_streams(const void* table, int table_dtype, const int* ids, float* out, int tokens,
+                                int hidden, int vocab, int copies, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0 && copies >= 1,
+                 "embed_streams: bad sizes tokens=%d hidden=%d vocab=%d copies=%d", tokens, hidden, vocab, copies);
+    if (tokens == 0) return 0;
+    if (table_dtype == MRUN_F32)
+        embed_streams_kernel<float><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, copies);
+    else if (table_dtype == MRUN_BF16)
+        embed_streams_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out,
+                                                                         hidden, vocab, copies);
+    else
+        return mrun_set_error("embed_streams: unknown dtype code %d", table_dtype);
+    MRUN_CHECK_LAUNCH("embed_streams");
+    return 0;
+}
+
+// streams: float32 [tokens, S, width].  y: float32 [tokens, width] or null.  mix: [S, S] indexed
+// [from, to]; out_c, in_c: [S] (null: ones).  norm_w: float32 [width] or null.  h_out: [n_rows,
+// width] in out_dtype (needed with norm_w); u_out: float32 [n_rows, width] or null.
+MRUN_API int mrun_streams_step(float* streams, const float* y, const float* mix, const float* out_c,
+                               const float* in_c, const float* norm_w, float eps, void* h_out, int out_dtype,
+                               float* u_out, const int* rows, int n_rows, int S, int width, cudaStream_t stream) {
+    MRUN_REQUIRE(n_rows >= 0 && width > 0, "streams_step: bad sizes rows=%d width=%d", n_rows, width);
+    MRUN_REQUIRE(S >= 1 && S <= MAX_STREAMS, "streams_step: %d streams, the kernel takes 1 to %d", S, MAX_STREAMS);
+    MRUN_REQUIRE(width <= 12000, "streams_step: width=%d exceeds the supported 12000", width);
+    MRUN_REQUIRE(norm_w == nullptr || h_out != nullptr, "streams_step: a norm needs an output");
+    MRUN_REQUIRE(norm_w != nullptr || u_out != nullptr, "streams_step: nothing to write");
+    if (n_rows == 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (out_dtype == MRUN_F32)
+        streams_step_kernel<float><<<n_rows, 256, smem, stream>>>(streams, y, mix, out_c, in_c, norm_w, eps,
+                                                                   (float*)h_out, u_out, rows, S, width);
+    else if (out_dtype == MRUN_BF16)
+        streams_step_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(
+            streams, y, mix, out_c, in_c, norm_w, eps, (__nv_bfloat16*)h_out, u_out, rows, S, width);
+    else
+        return mrun_set_error("streams_step: unknown dtype code %d", out_dtype);
+    MRUN_CHECK_LAUNCH("streams_step");
+    return 0;
+}

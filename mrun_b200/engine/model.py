@@ -21,6 +21,8 @@ from .batch import StepContext
 class Model:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], runtime: Runtime):
         spec.validate()
+        if spec.streams < 1 or (spec.streams > 1 and spec.embedding_transform is not None):
+            raise ValueError("a model has at least one residual stream; an embedding transform takes one stream")
         self.spec = spec
         self.runtime = runtime
         self.embedding = runtime.matrix(tensors[spec.embedding_name])
@@ -43,8 +45,10 @@ class Model:
         """The need of each schedule entry (None for entries that read another's cache)."""
         needs = []
         for entry in self.order:
-            mixer = self.blocks[entry.layer].mixer
-            needs.append(None if entry.cache_of is not None else mixer.cache_need())
+            block = self.blocks[entry.layer]
+            # a block that keeps state of its own (an input convolution) states the need itself
+            owner = block if hasattr(block, "cache_need") else block.mixer
+            needs.append(None if entry.cache_of is not None else owner.cache_need())
         return needs
 
     def cache_shares(self) -> List[Optional[int]]:
@@ -92,9 +96,12 @@ class Model:
     def hidden_states(self, ctx: StepContext, caches) -> tuple:
         """Runs the layers; returns the 32-bit stream and the last branch output not yet added."""
         ops.RowSums.begin_step(self.runtime.device)
-        resid = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=torch.float32,
+        resid = torch.empty((ctx.num_tokens, self.spec.streams * self.spec.hidden_size), dtype=torch.float32,
                             device=self.runtime.device)
-        ops.embed(self.embedding, ctx.token_ids, resid)
+        if self.spec.streams > 1:           # every stream starts as the embedding's row
+            ops.embed_streams(self.embedding, ctx.token_ids, resid, self.spec.streams)
+        else:
+            ops.embed(self.embedding, ctx.token_ids, resid)
         if self.embedding_transform is not None:
             resid = self.embedding_transform.forward(resid)
         delta = None
@@ -107,9 +114,15 @@ class Model:
 
     def logits(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """float32 ``[len(rows), vocab]``: final norm and head at the wanted rows only."""
-        if isinstance(delta, ops.PENDING) and not getattr(self.final_norm, "accepts_pending", False):
-            delta = delta.compute()
-        h = self.final_norm.rows_forward(resid, delta, rows)
+        if isinstance(delta, ops.PendingStreams) or self.spec.streams > 1:
+            # the last sublayer's write and the sum of the streams, at the wanted rows only
+            total = ops.streams_step(resid, delta, None, None, 0.0, torch.float32, self.spec.streams, rows=rows,
+                                     want_sum=True)
+            h = self.final_norm.add_forward(total, None)
+        else:
+            if isinstance(delta, ops.PENDING) and not getattr(self.final_norm, "accepts_pending", False):
+                delta = delta.compute()
+            h = self.final_norm.rows_forward(resid, delta, rows)
         logits = ops.linear(h, self.head, out_dtype=torch.float32)
         if self.logits_transform is not None:
             logits = self.logits_transform.forward(logits)

@@ -736,6 +736,13 @@ def soft_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
+def scale(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place on float32."""
+    _check(x, "x", torch.float32)
+    _lib.core().call("mrun_scale_f32", _ptr(x), _c_long(x.numel()), _c_float(factor), _stream())
+    return x
+
+
 # ------------------------------------------------------------------ a routed feed-forward's rows sorted by expert
 
 def moe_sort(chosen: torch.Tensor, weights: torch.Tensor):
@@ -800,3 +807,263 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, ends: torch.Tensor) -> torc
     be a strided view as long as ``in`` has unit stride."""
     _check(x, "x", torch.bfloat16); _check(w, "w", torch.bfloat16, dense=False); _check(ends, "ends", torch.int32)
     return torch.nn.functional.grouped_mm(x, w.transpose(-2, -1), offs=ends)
+
+
+# ------------------------------------------------------------------ several residual streams a token
+
+def embed_streams(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, copies: int) -> torch.Tensor:
+    """out[t, s] = float(table[ids[t]]) for each of the ``copies`` streams; out is float32
+    [tokens, copies * hidden]."""
+    _check(table, "table"); _check(ids, "ids", torch.int32); _check(out, "out", torch.float32)
+    vocab, hidden = table.shape
+    tokens = ids.numel()
+    if out.shape != (tokens, copies * hidden):
+        raise KernelError(f"embed_streams: out is {tuple(out.shape)}, expected {(tokens, copies * hidden)}")
+    _lib.core().call("mrun_embed_streams", _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), _c_int(tokens),
+                     _c_int(hidden), _c_int(vocab), _c_int(copies), _stream())
+    return out
+
+
+class PendingStreams:
+    """A sublayer's output (float32 rows) that has not been written into the token's streams yet,
+    with the coefficients of the write: x_t <- sum_s mix[s, t] x_s + out[t] * y (``mix`` and
+    ``out`` None: the plain residual sum).  The next read of the streams applies it
+    (:func:`streams_step`)."""
+
+    def __init__(self, y: torch.Tensor, mix: Optional[torch.Tensor], out: Optional[torch.Tensor]):
+        self.y, self.mix, self.out = y, mix, out
+
+
+def streams_step(streams: torch.Tensor, pending: Optional[PendingStreams], in_c: Optional[torch.Tensor],
+                 norm_weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, count: int,
+                 rows: Optional[torch.Tensor] = None, want_sum: bool = False):
+    """Applies the pending write to the ``count`` streams of every token (float32 [tokens, count *
+    width], in place), forms u = sum_s in_c[s] x_s (``in_c`` None: the plain sum) and returns its
+    RMS norm times ``norm_weight`` in ``out_dtype`` (``want_sum``: the 32-bit u itself instead).
+    With ``rows`` (int32) only those tokens are read and the streams stay as they are."""
+    _check(streams, "streams", torch.float32)
+    tokens = streams.shape[0]
+    width = streams.shape[1] // count
+    n_rows = tokens if rows is None else rows.numel()
+    y = mix = out_c = None
+    if pending is not None:
+        y, mix, out_c = pending.y, pending.mix, pending.out
+        _check(y, "y", torch.float32)
+        if y.shape != (tokens, width):
+            raise KernelError(f"streams_step: the pending output is {tuple(y.shape)}, expected {(tokens, width)}")
+        for name, c, n in (("mix", mix, count * count), ("out", out_c, count)):
+            if c is not None:
+                _check(c, name, torch.float32)
+                if c.numel() != n:
+                    raise KernelError(f"streams_step: {name} has {c.numel()} entries, expected {n}")
+    if in_c is not None:
+        _check(in_c, "in", torch.float32)
+        if in_c.numel() != count:
+            raise KernelError(f"streams_step: in has {in_c.numel()} entries, expected {count}")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    h = u = None
+    if want_sum:
+        u = torch.empty((n_rows, width), dtype=torch.float32, device=streams.device)
+    else:
+        _check(norm_weight, "norm_weight", torch.float32)
+        if norm_weight.numel() != width:
+            raise KernelError(f"streams_step: the norm weight has {norm_weight.numel()} entries, the width is {width}")
+        h = torch.empty((n_rows, width), dtype=out_dtype, device=streams.device)
+    _lib.core().call("mrun_streams_step", _ptr(streams), _ptr(y), _ptr(mix), _ptr(out_c), _ptr(in_c),
+                     _ptr(None if want_sum else norm_weight), _c_float(eps), _ptr(h),
+                     _c_int(dtype_code(out_dtype if h is not None else torch.float32)), _ptr(u), _ptr(rows),
+                     _c_int(n_rows), _c_int(count), _c_int(width), _stream())
+    return u if want_sum else h
+
+
+# ------------------------------------------------------------------ recurrent mixers
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, ctx, residual: bool, silu: bool) -> torch.Tensor:
+    """Causal convolution per channel over each request's tokens (the last tap meets the token
+    itself), added to x (``residual``) and/or passed through SiLU.  ``x``: [tokens, channels],
+    rows may be strided; ``weight``: float32 [channels, taps]; ``state``: [slots, taps - 1,
+    channels] in x's dtype, the request's last inputs, read and left up to date."""
+    _check(x, "x", dense=False); _check(weight, "weight", torch.float32); _check(state, "state", x.dtype)
+    tokens, channels = x.shape
+    taps = weight.shape[1]
+    if x.stride(1) != 1 or weight.shape[0] != channels or state.shape[1:] != (taps - 1, channels):
+        raise KernelError(f"causal_conv: x {tuple(x.shape)}, weight {tuple(weight.shape)}, state {tuple(state.shape)}")
+    out = torch.empty((tokens, channels), dtype=x.dtype, device=x.device)
+    _lib.core().call("mrun_causal_conv", _ptr(x), _c_long(x.stride(0)), _ptr(weight), _ptr(state), _ptr(out),
+                     _c_long(channels), dtype_code(x.dtype), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot),
+                     _c_int(ctx.num_segments), _c_int(ctx.max_q_len), _c_int(channels), _c_int(taps),
+                     _c_int(1 if residual else 0), _c_int(1 if silu else 0), _stream())
+    return out
+
+
+def _strided_rows(t: torch.Tensor, name: str) -> int:
+    _check(t, name, dense=False)
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be rows of contiguous features")
+    return t.stride(0)
+
+
+def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, ctx,
+               heads: int, dim: int, vdim: int, silu_inputs: bool) -> torch.Tensor:
+    """Per head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over each request's tokens, from
+    and into ``state`` (float32 [slots, heads, dim, vdim]).  q, k, v: column slices of one matrix
+    of rows.  Returns float32 [tokens, heads * vdim]."""
+    ld = _strided_rows(q, "q")
+    if _strided_rows(k, "k") != ld or _strided_rows(v, "v") != ld or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("decay_scan: q, k and v must be slices of one matrix")
+    _check(decay, "decay", torch.float32); _check(state, "state", torch.float32)
+    tokens = q.shape[0]
+    if q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * vdim \
+            or state.shape[1:] != (heads, dim, vdim) or decay.numel() != heads:
+        raise KernelError("decay_scan: sizes do not match")
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
+    _lib.core().call("mrun_decay_scan", _ptr(q), _ptr(k), _ptr(v), _c_long(ld), dtype_code(q.dtype), _ptr(decay),
+                     _ptr(state), _ptr(out), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), _c_int(ctx.num_segments),
+                     _c_int(heads), _c_int(dim), _c_int(vdim), _c_int(1 if silu_inputs else 0), _stream())
+    return out
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, ctx, heads: int, kv_heads: int,
+               dim: int, vdim: int) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel over each request's tokens (see
+    ``csrc/recurrent.cu``).  q, k ([tokens, kv_heads * dim]) and v ([tokens, heads * vdim]):
+    column slices of one matrix; ``a``: float32 [tokens, heads * dim]; ``b``: [tokens, heads],
+    rows may be strided.  Returns float32 [tokens, heads * vdim]."""
+    ld = _strided_rows(q, "q")
+    if _strided_rows(k, "k") != ld or _strided_rows(v, "v") != ld or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("delta_scan: q, k and v must be slices of one matrix")
+    ldb = _strided_rows(b, "b")
+    _check(a, "a", torch.float32); _check(a_log, "a_log", torch.float32); _check(dt_bias, "dt_bias", torch.float32)
+    _check(state, "state", torch.float32)
+    tokens = q.shape[0]
+    if q.shape[1] != kv_heads * dim or k.shape[1] != kv_heads * dim or v.shape[1] != heads * vdim \
+            or a.shape != (tokens, heads * dim) or b.shape != (tokens, heads) or b.dtype != q.dtype \
+            or a_log.numel() != heads or dt_bias.numel() != heads * dim or state.shape[1:] != (heads, dim, vdim):
+        raise KernelError("delta_scan: sizes do not match")
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
+    _lib.core().call("mrun_delta_scan", _ptr(q), _ptr(k), _ptr(v), _c_long(ld), dtype_code(q.dtype),
+                     _c_int(heads // kv_heads), _ptr(a), _ptr(b), _c_long(ldb), _ptr(a_log), _ptr(dt_bias), _ptr(state),
+                     _ptr(out), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), _c_int(ctx.num_segments), _c_int(heads),
+                     _c_int(dim), _c_int(vdim), _stream())
+    return out
+
+
+def gated_norm(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, groups: int,
+               out_dtype: torch.dtype) -> torch.Tensor:
+    """Per group of ``o.shape[1] // groups`` features: o / sqrt(mean(o^2) + eps) * weight *
+    sigmoid(gate).  ``o``: float32 [tokens, features]; ``weight``: float32, one entry per feature
+    of a row or of a group; ``gate``: [tokens, features] in ``out_dtype``, rows may be strided."""
+    _check(o, "o", torch.float32); _check(weight, "weight", torch.float32)
+    ldg = _strided_rows(gate, "gate")
+    tokens, features = o.shape
+    n = features // groups
+    if gate.shape != o.shape or gate.dtype != out_dtype or weight.numel() not in (n, features) or n * groups != features:
+        raise KernelError("gated_norm: sizes do not match")
+    out = torch.empty((tokens, features), dtype=out_dtype, device=o.device)
+    _lib.core().call("mrun_gated_norm", _ptr(o), _ptr(weight), _c_int(weight.numel()), _ptr(gate), _c_long(ldg),
+                     dtype_code(out_dtype), _c_float(eps), _ptr(out), _c_int(tokens), _c_int(groups), _c_int(n), _stream())
+    return out
+
+
+# ------------------------------------------------------------------ differential attention
+
+def diff_rope_cache(qkv: torch.Tensor, rot: Optional[torch.Tensor], rot_dims: int, slots: Optional[torch.Tensor],
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                    page_size: int) -> None:
+    """Rotates the q and k vectors of ``qkv`` ([tokens, 2 heads dim | 2 kv_heads dim | kv_heads
+    vdim], maps outermost) in place and stores k and v in the pages ``slots`` names (key pages
+    [2, pages, kv_heads, page, dim], value pages [chunks, pages, kv_heads, page, vdim / chunks])."""
+    _check(qkv, "qkv"); _check(k_cache, "k_cache", qkv.dtype); _check(v_cache, "v_cache", qkv.dtype)
+    tokens = qkv.shape[0]
+    chunks, pages = v_cache.shape[0], v_cache.shape[1]
+    if k_cache.shape != (2, pages, kv_heads, page_size, dim) or v_cache.shape != (chunks, pages, kv_heads, page_size, vdim // chunks) \
+            or qkv.shape[1] != 2 * heads * dim + 2 * kv_heads * dim + kv_heads * vdim:
+        raise KernelError("diff_rope_cache: sizes do not match")
+    if rot is not None:
+        _check(rot, "rot", torch.float32)
+        if rot.shape != (tokens, rot_dims // 2, 2):
+            raise KernelError(f"diff_rope_cache: rot is {tuple(rot.shape)}")
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+    _lib.core().call("mrun_diff_rope_cache", _ptr(qkv), _c_long(qkv.stride(0)), dtype_code(qkv.dtype), _ptr(rot),
+                     _c_int(rot_dims if rot is not None else 0), _ptr(slots), _ptr(k_cache), _ptr(v_cache), _c_long(pages),
+                     _c_int(tokens), _c_int(heads), _c_int(kv_heads), _c_int(dim), _c_int(vdim), _c_int(vdim // chunks),
+                     _c_int(page_size), _stream())
+
+
+def diff_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                   token_slot: torch.Tensor, positions: torch.Tensor, heads: int, vdim: int, scale: float,
+                   lam: float, eps: float, out_scale: float, window: int = 0) -> torch.Tensor:
+    """Both maps of a differential attention, their combination a1 - lam * a2 and the head norm
+    (times ``out_scale``) in one kernel on CUDA cores, 32-bit arithmetic.  ``q``: rows [2, heads,
+    dim], may be a column slice of a wider matrix."""
+    ld = _strided_rows(q, "q")
+    _check(k_cache, "k_cache", q.dtype); _check(v_cache, "v_cache", q.dtype)
+    _check(block_tables, "block_tables", torch.int32); _check(token_slot, "token_slot", torch.int32)
+    _check(positions, "positions", torch.int32)
+    maps, pages, kv_heads, page_size, dim = k_cache.shape
+    tokens = positions.numel()
+    if maps != 2 or q.shape != (tokens, 2 * heads * dim) or v_cache.shape[1:4] != (pages, kv_heads, page_size) \
+            or v_cache.shape[0] * v_cache.shape[4] != vdim:
+        raise KernelError("diff_attention: sizes do not match")
+    out = torch.empty((tokens, heads * vdim), dtype=q.dtype, device=q.device)
+    _lib.core().call("mrun_diff_attention", _ptr(q), _c_long(ld), _ptr(out), _ptr(k_cache), _ptr(v_cache),
+                     dtype_code(q.dtype), _ptr(block_tables), _c_int(block_tables.shape[1]), _ptr(token_slot),
+                     _ptr(positions), _c_long(pages), _c_int(tokens), _c_int(heads), _c_int(kv_heads), _c_int(dim),
+                     _c_int(vdim), _c_int(v_cache.shape[4]), _c_int(page_size), _c_float(scale), _c_float(lam),
+                     _c_float(eps), _c_float(out_scale), _c_int(window), _stream())
+    return out
+
+
+def diff_combine(maps: torch.Tensor, heads: int, vdim: int, lam: float, eps: float, out_scale: float) -> torch.Tensor:
+    """``maps``: [2, chunks, tokens, heads * vdim / chunks], the maps' outputs chunk by chunk;
+    returns (a1 - lam * a2) / rms over each head's ``vdim`` values * ``out_scale``."""
+    _check(maps, "maps")
+    two, chunks, tokens, row = maps.shape
+    if two != 2 or row * chunks != heads * vdim:
+        raise KernelError("diff_combine: sizes do not match")
+    out = torch.empty((tokens, heads * vdim), dtype=maps.dtype, device=maps.device)
+    _lib.core().call("mrun_diff_combine", _ptr(maps), _ptr(out), dtype_code(maps.dtype), _c_int(tokens), _c_int(heads),
+                     _c_int(vdim), _c_int(vdim // chunks), _c_float(lam), _c_float(eps), _c_float(out_scale), _stream())
+    return out
+
+
+# ------------------------------------------------------------------ experts chosen by a table
+
+def table_route(token_ids: torch.Tensor, table: torch.Tensor, experts: int, chosen: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [tokens, experts]: 1 / top at the experts that row ``token id`` of ``table`` (int32
+    [vocab, top]) names, zero elsewhere; ``chosen`` (int32 [tokens, top]) gets the experts."""
+    _check(token_ids, "token_ids", torch.int32); _check(table, "table", torch.int32)
+    tokens = token_ids.numel()
+    vocab, top = table.shape
+    weights = torch.empty((tokens, experts), dtype=torch.float32, device=token_ids.device)
+    if chosen is not None:
+        _check(chosen, "chosen", torch.int32)
+        if chosen.shape != (tokens, top):
+            raise KernelError(f"table_route: chosen is {tuple(chosen.shape)}, expected {(tokens, top)}")
+    _lib.core().call("mrun_table_route", _ptr(token_ids), _ptr(table), _ptr(weights), _ptr(chosen), _c_int(tokens),
+                     _c_int(vocab), _c_int(experts), _c_int(top), _stream())
+    return weights
+
+
+def clamped_glu(u: torch.Tensor, weights: Optional[torch.Tensor], blocks: int, ff: int, limit: float, alpha: float) -> torch.Tensor:
+    """``u``: [rows, blocks * 2 * ff], a block of [gate | up] columns per expert.  Returns [rows,
+    blocks * ff]: min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, +-limit) + 1),
+    times ``weights[row, block]`` (float32 [rows, blocks]) or ``weights[row]`` (float32 [rows])."""
+    _check(u, "u")
+    rows = u.shape[0]
+    if u.shape[1] != blocks * 2 * ff:
+        raise KernelError(f"clamped_glu: u is {tuple(u.shape)}, expected width {blocks * 2 * ff}")
+    per_block = 0
+    if weights is not None:
+        _check(weights, "weights", torch.float32)
+        if weights.shape == (rows, blocks) and weights.dim() == 2:
+            per_block = 1
+        elif weights.numel() != rows:
+            raise KernelError(f"clamped_glu: weights {tuple(weights.shape)}")
+    act = torch.empty((rows, blocks * ff), dtype=u.dtype, device=u.device)
+    _lib.core().call("mrun_clamped_glu", _ptr(u), _ptr(act), dtype_code(u.dtype), _ptr(weights), _c_int(per_block),
+                     _c_int(rows), _c_int(blocks), _c_int(ff), _c_float(limit), _c_float(alpha), _stream())
+    return act

@@ -1,5 +1,6 @@
 """Parts a layer is assembled from.  Importing the package registers the built-in kinds."""
-from . import attention, block, feedforward, latent_attention, norm, rotary, routed, transforms  # noqa: F401  (registration)
+from . import (attention, block, channel_delta, decay_attention, differential_attention, feedforward, latent_attention,
+               norm, rotary, routed, table_routed, transforms)  # noqa: F401  (registration)
 from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, TRANSFORMS, Precision, Runtime,
                    register_arrangement, register_feed_forward, register_mixer, register_norm,
                    register_position, register_transform)

@@ -17,6 +17,7 @@ from typing import Optional
 
 import torch
 
+from ..cache.needs import FixedState
 from ..config.spec import LayerSpec, TensorSpec
 from ..kernels import ops
 from .base import FEED_FORWARDS, MIXERS, NORMS, Runtime, local, register_arrangement
@@ -136,3 +137,107 @@ class SandwichBlock:
         else:
             f = self.feed_forward.forward(h, ctx)
         return self._branch(f, self.feed_forward_post_norm)
+
+
+@register_arrangement("streams")
+class StreamsBlock:
+    """A pre-norm layer over several residual streams a token (hyper-connections).  The stream
+    tensor is float32 [tokens, S * width].  Sublayer i (1: the mixer, 2: the feed-forward) reads u =
+    sum_s in_i[s] x_s through its norm and writes x_t <- sum_s mix_i[s, t] x_s + out_i[t] * y into
+    all streams at once.  The write is handed on unapplied (``ops.PendingStreams``) and runs in
+    the kernel that makes the next sublayer's input, so a sublayer boundary is one kernel.  With
+    ``LayerSpec.streams`` = 0 the layer has no coefficients and this is ``x += y`` over one
+    stream.
+
+    ``LayerSpec.input_conv_taps`` > 0: what the mixer reads is h + conv(h), a causal convolution
+    per channel over the request's tokens; the last taps - 1 rows of h are per-request state of
+    this layer run, kept beside the mixer's own cache (``cache.states['input_conv']``).  A layer
+    without a feed-forward has the first half only."""
+
+    accepts_pending = False
+
+    @staticmethod
+    def tensor_specs(spec: LayerSpec, prefix: str = "") -> list[TensorSpec]:
+        p, s = spec.prefix, spec.streams
+        out = (NORMS.tensor_specs(spec.mixer_norm, f"{p}.{spec.mixer_norm_prefix}")
+               + MIXERS.tensor_specs(spec.mixer, f"{p}.{spec.mixer_prefix}"))
+        halves = [spec.mixer_streams_prefix]
+        if spec.feed_forward is not None:
+            out += (NORMS.tensor_specs(spec.feed_forward_norm, f"{p}.{spec.feed_forward_norm_prefix}")
+                    + FEED_FORWARDS.tensor_specs(spec.feed_forward, f"{p}.{spec.feed_forward_prefix}"))
+            halves.append(spec.feed_forward_streams_prefix)
+        if s:
+            for half in halves:
+                out += [TensorSpec(f"{p}.{half}.in", (s,), "streams_in"), TensorSpec(f"{p}.{half}.out", (s,), "norm"),
+                        TensorSpec(f"{p}.{half}.mix", (s, s), "streams_mix")]
+        if spec.input_conv_taps:
+            out.append(TensorSpec(f"{p}.{spec.input_conv_name}", (spec.mixer_norm.size, spec.input_conv_taps)))
+        return out
+
+    def __init__(self, spec: LayerSpec, tensors, runtime: Runtime):
+        mine = local(tensors, spec.prefix)
+        self.count = max(1, spec.streams)
+        self.act = runtime.precision.act
+        self.mixer_norm = NORMS.build(spec.mixer_norm, local(mine, spec.mixer_norm_prefix), runtime)
+        self.mixer = MIXERS.build(spec.mixer, local(mine, spec.mixer_prefix), runtime)
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, local(mine, spec.feed_forward_norm_prefix), runtime)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, local(mine, spec.feed_forward_prefix), runtime)
+        self._feed_forward_defers = bool(getattr(self.feed_forward, "can_defer_output", False))
+        self._mixer_defers = bool(getattr(self.mixer, "can_defer_output", False))
+
+        def coefficients(prefix):
+            if not spec.streams:
+                return None, None, None
+            c = local(mine, prefix)
+            return runtime.vector_f32(c["in"]), runtime.vector_f32(c["mix"]), runtime.vector_f32(c["out"])
+
+        self.in1, self.mix1, self.out1 = coefficients(spec.mixer_streams_prefix)
+        self.in2, self.mix2, self.out2 = coefficients(spec.feed_forward_streams_prefix) if self.feed_forward else (None,) * 3
+        self.taps = int(spec.input_conv_taps)
+        self.width = spec.mixer_norm.size
+        self.conv_weight = runtime.vector_f32(mine[spec.input_conv_name]) if self.taps else None
+        self._state_dtype = runtime.precision.name
+
+    def cache_need(self):
+        """The mixer's need and, with an input convolution, the state of its last inputs."""
+        need = self.mixer.cache_need()
+        if not self.taps:
+            return need
+        own = FixedState((self.taps - 1, self.width), self._state_dtype, name="input_conv")
+        if need is None:
+            return (own,)
+        return (tuple(need) if isinstance(need, (tuple, list)) else (need,)) + (own,)
+
+    @staticmethod
+    def _rows(y) -> torch.Tensor:
+        """A sublayer's output as 32-bit rows (its last product writes them where it was left unrun)."""
+        if isinstance(y, ops.PendingLinear):
+            return ops.linear(y.x, y.w, out_dtype=torch.float32)
+        if isinstance(y, ops.PENDING):
+            y = y.compute()
+        return y if y.dtype == torch.float32 else y.to(torch.float32)
+
+    def forward(self, resid: torch.Tensor, delta, ctx, cache):
+        if delta is not None and not isinstance(delta, ops.PendingStreams):
+            delta = ops.PendingStreams(self._rows(delta), None, None)
+        h = ops.streams_step(resid, delta, self.in1, self.mixer_norm.weight, self.mixer_norm.eps, self.act, self.count)
+        if self.taps:
+            if cache is None or not cache.writable:
+                raise ValueError("a layer with an input convolution needs a cache of its own")
+            h = ops.causal_conv(h, self.conv_weight, cache.states["input_conv"], ctx, residual=True, silu=False)
+        if self._mixer_defers:
+            a = self.mixer.forward(h, ctx, cache, defer_output=True)
+        else:
+            a = self.mixer.forward(h, ctx, cache)
+        a = ops.PendingStreams(self._rows(a), self.mix1, self.out1)
+        if self.feed_forward is None:
+            return a
+        h = ops.streams_step(resid, a, self.in2, self.feed_forward_norm.weight, self.feed_forward_norm.eps, self.act,
+                             self.count)
+        if self._feed_forward_defers:
+            f = self.feed_forward.forward(h, ctx, defer_output=True)
+        else:
+            f = self.feed_forward.forward(h, ctx)
+        return ops.PendingStreams(self._rows(f), self.mix2, self.out2)

@@ -16,7 +16,7 @@ from .base import Runtime, register_norm
 class RMSNorm:
     @staticmethod
     def tensor_specs(spec: RMSNormSpec, prefix: str):
-        return [TensorSpec(prefix if spec.bare else f"{prefix}.weight", (spec.size,), "norm")]
+        return [TensorSpec(prefix if spec.bare else f"{prefix}.weight", () if spec.scalar else (spec.size,), "norm")]
 
     # ``delta`` may be a product that has not run yet (``ops.PendingLinear``): with a handful
     # of rows it runs with the residual sum and this norm folded into its epilogue, and what
@@ -26,7 +26,10 @@ class RMSNorm:
 
     def __init__(self, spec: RMSNormSpec, tensors, runtime: Runtime):
         self.size, self.eps = spec.size, float(spec.eps)
-        self.weight = runtime.vector_f32(tensors["" if spec.bare else "weight"])
+        weight = tensors["" if spec.bare else "weight"]
+        if spec.scalar:             # one number for all coordinates: the kernels take it as a vector of equal entries
+            weight = weight.reshape(1).expand(spec.size)
+        self.weight = runtime.vector_f32(weight)
         self.act = runtime.precision.act
 
     def add_forward(self, resid: torch.Tensor, delta):

@@ -2,7 +2,7 @@
 ``ModelSpec.logits_transform``)."""
 from __future__ import annotations
 
-from ..config.spec import SoftCapSpec
+from ..config.spec import ScaleSpec, SoftCapSpec
 from ..kernels import ops
 from .base import Runtime, register_transform
 
@@ -22,3 +22,18 @@ class SoftCap:
 
     def forward(self, x):
         return ops.soft_cap(x, self.cap)
+
+
+@register_transform("scale")
+class Scale:
+    """``factor * x`` on float32, in place."""
+
+    @staticmethod
+    def tensor_specs(spec: ScaleSpec, prefix: str):
+        return []
+
+    def __init__(self, spec: ScaleSpec, tensors, runtime: Runtime):
+        self.factor = float(spec.factor)
+
+    def forward(self, x):
+        return ops.scale(x, self.factor)

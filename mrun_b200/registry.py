@@ -65,8 +65,10 @@ def load_config(model_dir: str):
 def _register_builtin() -> None:
     from .config.qwen3 import Qwen3Config
     from .config.zasesun import ZasesunConfig
+    from .config.balivik import BalivikConfig
     register_architecture(Qwen3Config)
     register_architecture(ZasesunConfig)
+    register_architecture(BalivikConfig)
 
 
 _register_builtin()

@@ -3,7 +3,9 @@ and a seed.
 
 Each tensor has a generator of its own, seeded from (seed, tensor name), so a tensor's values do
 not depend on which other tensors exist or on their order.  Matrices and tables are N(0, std);
-scale vectors of norms are 1, or 1 + N(0, norm_noise).  The reference's test helper fills its tiny
+scale vectors of norms are 1, or 1 + N(0, norm_noise); the few other kinds (an integer table of
+distinct entries per row, weights between residual streams, logarithms of decay rates) are named
+by ``TensorSpec.init``.  The reference's test helper fills its tiny
 model the same way with its own generator (crates/mrun-engine/src/testing.rs:42-51, 91-149).
 """
 from __future__ import annotations
@@ -34,6 +36,19 @@ def random_tensor(t: TensorSpec, seed: int, std: float, norm_noise: float, dtype
             return torch.ones(t.shape, dtype=dtype, device=device)
         noise = torch.randn(t.shape, generator=gen, dtype=torch.float32, device=device)
         return (1.0 + norm_noise * noise).to(dtype)
+    if t.init.startswith("table:"):
+        # every row names different entries of range(n), as many as the row is long
+        n = int(t.init.split(":")[1])
+        order = torch.rand((t.shape[0], n), generator=gen, dtype=torch.float32, device=device).argsort(dim=1)
+        return order[:, :t.shape[1]].to(torch.int32).contiguous()
+    if t.init == "streams_in":          # reading weights of several residual streams: about an even share each
+        noise = torch.randn(t.shape, generator=gen, dtype=torch.float32, device=device)
+        return (1.0 / t.shape[0] + 0.2 * noise).to(dtype)
+    if t.init == "streams_mix":         # stream-to-stream weights: near the identity
+        noise = torch.randn(t.shape, generator=gen, dtype=torch.float32, device=device)
+        return (torch.eye(t.shape[0], dtype=torch.float32, device=device) + 0.15 * noise).to(dtype)
+    if t.init == "log_rate":            # logarithms of decay rates between e^-3 and 1
+        return (torch.rand(t.shape, generator=gen, dtype=torch.float32, device=device) * 3.0 - 3.0).to(dtype)
     if t.init != "normal":
         raise ValueError(f"tensor {t.name}: unknown init {t.init!r}")
     if device == "cpu" or len(t.shape) < 2:
