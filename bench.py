@@ -3,7 +3,7 @@
 random weights and seeded synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
-                    [--shape 8b|4b|32b] [--serve] [--design zasesun]
+                    [--shape 8b|4b|32b] [--serve] [--design zasesun|balivik]
 
 A *step* is one decode step of a batch of 8 requests that each hold 1,024 tokens of context.
 ``value`` is decoded tokens per second over exactly K steps, timed on the device with CUDA events
@@ -281,25 +281,95 @@ def zasesun_counts(cfg: dict, tokens: int):
     return flops + 2.0 * cfg["vocab"] * h, row_bytes
 
 
+# Layer sizes for --design balivik: (Balivik sizes, the Qwen3 sizes of equal width, depth, head count
+# and dense feed-forward size).  Eight layers in the order decay attention, delta rule, two
+# differential attentions, twice (the second block's last layer is a decay attention); key
+# sizes of 64 and 128 (the differential attention's values are two chunks of its key size, so its
+# maps go through the tensor-core attention kernels), four residual streams, an input convolution
+# of four taps, dense and table-routed feed-forwards alternating (8 experts, 2 chosen).
+def _balivik_sizes(width, heads, kv_heads, att_dim, dim, ff, experts, top, expert_ff, rank, layers, vocab):
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": att_dim, "vdim": 2 * att_dim, "scale": att_dim ** -0.5, "diff": 0.3,
+           "rot": {"base": 10000.0, "dims": att_dim}}
+    lin = {"heads": heads, "dim": dim, "vdim": dim, "decay": [1.0 - 2.0 ** -(2 + 6 * i / max(1, heads - 1)) for i in range(heads)]}
+    delta = {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4, "decay_rank": rank, "gate_rank": rank}
+    kinds = [("lightning", lin), ("channel_delta", delta), ("attention", att), ("attention", att)]
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0}}
+    return {"architecture": "Balivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": 4,
+            "canon": {"taps": 4}, "logit_scale": 0.5,
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": dense if i % 2 == 0 else moe}
+                       for i in range(layers)]}
+
+
+BALIVIK_SIZES = {
+    "w2048": (_balivik_sizes(2048, 16, 4, 64, 128, 8192, 8, 2, 2048, 128, 8, 32768),
+              dict(QWEN3_8B, num_hidden_layers=8, hidden_size=2048, num_attention_heads=16, num_key_value_heads=4,
+                   head_dim=128, intermediate_size=8192, vocab_size=32768, tie_word_embeddings=False)),
+    "w4096": (_balivik_sizes(4096, 32, 8, 128, 128, 12288, 8, 2, 3072, 256, 8, 32768),
+              dict(QWEN3_8B, num_hidden_layers=8, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                   head_dim=128, intermediate_size=12288, vocab_size=32768, tie_word_embeddings=False)),
+}
+
+
+def balivik_counts(cfg: dict, tokens: int):
+    """(FLOPs of a prompt of ``tokens`` tokens as the design states them, bytes of one token's
+    cache rows over all layers, bytes of one request's recurrent states over all layers) of a
+    Balivik configuration: products count two FLOPs a weight and token (a table-routed layer its
+    chosen experts only), a differential attention both maps' scores and weighted sums for every
+    visible key, a recurrent mixer the update and the read-out of its state for every token."""
+    h, flops, row_bytes, state_bytes = cfg["width"], 0.0, 0, 0
+    for layer in cfg["layers"]:
+        m, kind = layer["mixer"], layer["type"]
+        if kind == "attention":
+            params = h * (2 * m["heads"] * m["dim"] + 2 * m["kv_heads"] * m["dim"] + m["kv_heads"] * m["vdim"]
+                          + m["heads"] * m["vdim"])
+            flops += 2.0 * (tokens * tokens / 2.0) * m["heads"] * 2 * (m["dim"] + m["vdim"])
+            row_bytes += 2 * m["kv_heads"] * (2 * m["dim"] + m["vdim"])
+        elif kind == "lightning":
+            params = h * (2 * m["heads"] * m["dim"] + 3 * m["heads"] * m["vdim"])
+            flops += 2.0 * tokens * m["heads"] * 2 * m["dim"] * m["vdim"]
+            state_bytes += 4 * m["heads"] * m["dim"] * m["vdim"]
+        else:
+            inner, keyed = m["heads"] * m["vdim"], m["heads"] * m["dim"]
+            params = h * (2 * m["kv_heads"] * m["dim"] + 2 * inner + m["heads"] + m["decay_rank"] + m["gate_rank"]) \
+                + keyed * m["decay_rank"] + inner * m["gate_rank"]
+            flops += 2.0 * tokens * m["heads"] * 4 * m["dim"] * m["vdim"]
+            state_bytes += 4 * m["heads"] * m["dim"] * m["vdim"]
+        mlp = layer["mlp"]
+        if mlp and mlp["kind"] == "dense":
+            params += 3 * h * mlp["ff"]
+        elif mlp:
+            params += 3 * h * mlp["router"]["top"] * mlp["expert"]["ff"]
+        flops += 2.0 * tokens * params
+    return flops + 2.0 * cfg["vocab"] * h, row_bytes, state_bytes
+
+
 def compare_designs(args, peaks: dict) -> int:
-    """Prefill of 2,048 tokens and decode at batch 8 with 1,024-token contexts, Zasesun beside
-    Qwen3 at equal sizes, each through the same ``Executor.step`` and captured decode step."""
+    """Prefill of 2,048 tokens and decode at batch 8 with 1,024-token contexts, the named design
+    beside Qwen3 at equal sizes, each through the same ``Executor.step`` and captured decode step."""
     import torch
     from mrun_b200 import Engine
     from mrun_b200.config import Qwen3Config, ZasesunConfig
+    from mrun_b200.config.balivik import BalivikConfig
     from mrun_b200.engine import StepEntry
     context, batch = 1024, 8
     out = {}
     sampler = ClockSampler()
     sampler.start()
-    for name in (args.sizes.split(",") if args.sizes else sorted(DESIGN_SIZES)):
-        z_sizes, q_sizes = DESIGN_SIZES[name]
+    size_sets = DESIGN_SIZES if args.design == "zasesun" else BALIVIK_SIZES
+    for name in (args.sizes.split(",") if args.sizes else sorted(size_sets)):
+        z_sizes, q_sizes = size_sets[name]
         row = {}
-        for design in ("zasesun", "qwen3"):
+        for design in (args.design, "qwen3"):
+            state_bytes = 0
             if design == "zasesun":
                 config = ZasesunConfig.from_dict(z_sizes)
                 vocab, h = z_sizes["vocab"], z_sizes["width"]
                 flops, kv_bytes = zasesun_counts(z_sizes, PREFILL_TOKENS)
+            elif design == "balivik":
+                config = BalivikConfig.from_dict(z_sizes)
+                vocab, h = z_sizes["vocab"], z_sizes["width"]
+                flops, kv_bytes, state_bytes = balivik_counts(z_sizes, PREFILL_TOKENS)
             else:
                 config = Qwen3Config(**dict(q_sizes, max_position_embeddings=8192))
                 vocab, h, d = config.vocab_size, config.hidden_size, config.head_dim
@@ -331,7 +401,8 @@ def compare_designs(args, peaks: dict) -> int:
             decode_times, launches = time_decode(executor, requests, vocab, args.steps, args.warmup, repeats=2)
             ms = statistics.median(decode_times) / args.steps
             weight_bytes = executor.model.weight_bytes()
-            step_bytes = weight_bytes + batch * (context + args.warmup + args.steps) * kv_bytes
+            # recurrent states are read and written once a step and request
+            step_bytes = weight_bytes + batch * (context + args.warmup + args.steps) * kv_bytes + 2 * batch * state_bytes
             row[design] = {
                 "layers": len(executor.model.order), "weights_gb": round(weight_bytes / 1e9, 2),
                 "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
@@ -344,7 +415,7 @@ def compare_designs(args, peaks: dict) -> int:
             del engine, executor, requests
             torch.cuda.empty_cache()
         out[name] = row
-    print(json.dumps({"metric": "prefill and decode tok/s, Zasesun beside Qwen3 at equal sizes (bf16)", "unit": "tok/s",
+    print(json.dumps({"metric": f"prefill and decode tok/s, {args.design.capitalize()} beside Qwen3 at equal sizes (bf16)", "unit": "tok/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
                       "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
                       "config": {"prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "context": context,
@@ -382,7 +453,7 @@ def main() -> int:
     parser.add_argument("--profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                         help="bracket the timed decode steps (or the last timed prefill) with "
                              "cudaProfilerStart/Stop, for a profiler started with --profile-from-start off")
-    parser.add_argument("--design", choices=["zasesun"], default=None,
+    parser.add_argument("--design", choices=["zasesun", "balivik"], default=None,
                         help="instead of the default workload: the named design beside Qwen3 at equal sizes "
                              "(prefill of 2,048 tokens, decode at batch 8)")
     parser.add_argument("--sizes", default=None, help="with --design: which of its size sets to run, comma separated")

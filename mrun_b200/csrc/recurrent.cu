@@ -24,7 +24,7 @@ using namespace mrun;
 namespace {
 
 constexpr int MAX_TAPS = 8;
-constexpr int CONV_TILE = 64;       // tokens a block walks; at least MAX_TAPS - 1
+constexpr int CONV_TILE = 16;       // tokens a block walks; at least MAX_TAPS - 1
 
 template <bool EXACT> __device__ __forceinline__ float silu_f(float z) {
     if constexpr (EXACT) return z / (1.f + expf(-z));
@@ -88,127 +88,216 @@ causal_conv_kernel(const TA* __restrict__ x, long ldx, const float* __restrict__
 }
 
 // ------------------------------------------------------------------------------------------
-// The scans.  grid (value-column chunks of 32, heads, segments), block (32, DS): lane j owns
-// column j of the head's state, slice r the key rows r * DPT .. of it, DPT of them in registers.
-// The segment's tokens are staged TOKENS at a time into shared memory (q, k, the decays, the
-// block's 32 values, the write strengths), then walked one by one.  With DS > 1 the partial sums
-// of the slices meet in shared memory and are added in slice order.
+// The scans, in two kernels.
+//
+// scan_prepare (a block a token, nothing sequential): everything a token brings to the recurrence
+// as 32-bit rows: q and k per q/k head (through SiLU, or made unit vectors with q times D^-1/2),
+// v (through SiLU or as it is), and for the delta rule the decays g per head and key channel and
+// the write strengths beta.
+//
+// scan (grid: value-column groups x heads x segments, SCAN_WARPS warps a block): a warp's lanes
+// are R row slices x C = 32 / R columns; lane (r, c) owns up to 16 key rows of column c of the
+// head's state in registers; sums over the key rows meet by shuffles across the slices (a fixed
+// butterfly), and nothing in the walk waits for another warp.  The prepared rows of the segment's
+// tokens are copied `stage` at a time into one of two shared-memory buffers (asynchronous copies
+// of the next tokens run under the walk over the present ones); a slice's rows start on a
+// 16-byte boundary, one bank group after the slice before, and are read four at a time.
 // ------------------------------------------------------------------------------------------
-constexpr int SCAN_TOKENS = 8;
+constexpr int SCAN_WARPS = 4;
+constexpr int SCAN_ROWS = 16;       // key rows a lane holds at most
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-template <typename TA, int DPT, bool DELTA>
-__global__ void __launch_bounds__(64)
-scan_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long ld, int group,
-            const float* __restrict__ a, const TA* __restrict__ b, long ldb, const float* __restrict__ a_log,
-            const float* __restrict__ dt_bias, const float* __restrict__ decay, float* __restrict__ state,
-            float* __restrict__ out, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
-            int H, int D, int V, int silu_inputs) {
-    extern __shared__ float smem[];
-    const int lane = threadIdx.x, slice = threadIdx.y, DS = blockDim.y;
-    const int tid = slice * 32 + lane, nthreads = 32 * DS;
+template <typename TA>
+__global__ void __launch_bounds__(256)
+scan_prepare_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long ld,
+                    const float* __restrict__ a, const TA* __restrict__ b, long ldb, const float* __restrict__ a_log,
+                    const float* __restrict__ dt_bias, float* __restrict__ qf, float* __restrict__ kf,
+                    float* __restrict__ gf, float* __restrict__ vf, float* __restrict__ bf, int G, int H, int D, int V,
+                    int delta, int silu_inputs) {
+    const size_t t = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int head = warp; head < G; head += 8) {
+        const TA* qr = q + t * ld + (size_t)head * D;
+        const TA* kr = k + t * ld + (size_t)head * D;
+        float sq = 0.f, sk = 0.f;
+        for (int i = lane; i < D; i += 32) {
+            float qv = to_float(qr[i]), kv = to_float(kr[i]);
+            if (silu_inputs) { qv = silu_f<true>(qv); kv = silu_f<true>(kv); }
+            sq = fmaf(qv, qv, sq);
+            sk = fmaf(kv, kv, sk);
+        }
+        float fq = 1.f, fk = 1.f;
+        if (delta) {                // unit length per head (1e-6 inside the root), q times D^-1/2
+            sq = warp_sum(sq); sk = warp_sum(sk);
+            fq = (1.f / sqrtf((float)D)) / sqrtf(sq + 1e-6f);
+            fk = 1.f / sqrtf(sk + 1e-6f);
+        }
+        for (int i = lane; i < D; i += 32) {
+            float qv = to_float(qr[i]), kv = to_float(kr[i]);
+            if (silu_inputs) { qv = silu_f<true>(qv); kv = silu_f<true>(kv); }
+            qf[(t * G + head) * D + i] = qv * fq;
+            kf[(t * G + head) * D + i] = kv * fk;
+        }
+    }
+    for (int e = tid; e < H * V; e += 256) {
+        float vv = to_float(v[t * ld + e]);
+        if (silu_inputs) vv = silu_f<true>(vv);
+        vf[t * H * V + e] = vv;
+    }
+    if (delta) {
+        for (int e = tid; e < H * D; e += 256) {
+            const float step = softplus_f(a[t * H * D + e] + dt_bias[e]);
+            gf[t * H * D + e] = expf(-expf(a_log[e / D]) * step);
+        }
+        for (int e = tid; e < H; e += 256) bf[t * H + e] = 1.f / (1.f + expf(-to_float(b[t * ldb + e])));
+    }
+}
+
+template <int R> __device__ __forceinline__ float slices_sum(float v) {
+#pragma unroll
+    for (int o = 16; o >= 32 / R; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int R, bool DELTA>
+__global__ void __launch_bounds__(SCAN_WARPS * 32)
+scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const float* __restrict__ gf,
+            const float* __restrict__ vf, const float* __restrict__ bf, const float* __restrict__ decay,
+            float* __restrict__ state, float* __restrict__ out, const int* __restrict__ seg_q_start,
+            const int* __restrict__ seg_slot, int group, int G, int H, int D, int V, int stage) {
+    extern __shared__ __align__(16) float smem[];
+    constexpr int C = 32 / R, COLS = SCAN_WARPS * C, THREADS = SCAN_WARPS * 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int h = blockIdx.y, seg = blockIdx.z;
     const int q0 = seg_q_start[seg], n = seg_q_start[seg + 1] - q0;
     if (n <= 0) return;
-    const int col = blockIdx.x * 32 + lane;
+    const int r = lane / C, c = lane % C;
+    const int col0 = blockIdx.x * COLS, col = col0 + warp * C + c;
     const bool live = col < V;
-    const int kh = h / group;                    // the q/k head this head reads
-    float* qs = smem;                            // [SCAN_TOKENS][D]
-    float* ks = qs + SCAN_TOKENS * D;
-    float* gs = ks + SCAN_TOKENS * D;            // [SCAN_TOKENS][D] (DELTA)
-    float* vs = gs + (DELTA ? SCAN_TOKENS * D : 0);   // [SCAN_TOKENS][32]
-    float* bs = vs + SCAN_TOKENS * 32;           // [SCAN_TOKENS]
-    float* red = bs + SCAN_TOKENS;               // [DS][32]
+    const int per = (((D + R - 1) / R) + 3) & ~3;     // rows a slice, a multiple of 4, at most SCAN_ROWS
+    const int row0 = r * per;
+    const int mine = max(0, min(per, D - row0));
+    const int ps = per + 4, Dp = R * ps;              // row i of a staged vector sits at (i / per) * ps + i % per
+    const int kh = h / group;                         // the q/k head this head reads
+    const int vectors = DELTA ? 3 : 2;
+    const int buffer = stage * (vectors * Dp + COLS) + stage;         // floats of one buffer
 
-    float S[DPT];
+    float S[SCAN_ROWS];
     float* st = state + (((size_t)seg_slot[seg] * H + h) * D) * V + col;
-    const int row0 = slice * DPT;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) S[i] = (live && row0 + i < D) ? st[(size_t)(row0 + i) * V] : 0.f;
+    for (int i = 0; i < SCAN_ROWS; ++i) S[i] = (live && i < mine) ? st[(size_t)(row0 + i) * V] : 0.f;
     const float head_decay = DELTA ? 0.f : decay[h];
-    const float rate = DELTA ? expf(a_log[h]) : 0.f;
-    const float q_scale = DELTA ? rsqrtf((float)D) : 1.f;
 
-    for (int t0 = 0; t0 < n; t0 += SCAN_TOKENS) {
-        const int m = min(SCAN_TOKENS, n - t0);
-        __syncthreads();
-        for (int e = tid; e < m * D; e += nthreads) {
-            const int tt = e / D, i = e - tt * D;
-            const size_t row = (size_t)(q0 + t0 + tt);
-            float qv = to_float(q[row * ld + (size_t)kh * D + i]);
-            float kv = to_float(k[row * ld + (size_t)kh * D + i]);
-            if (silu_inputs) { qv = silu_f<true>(qv); kv = silu_f<true>(kv); }
-            qs[tt * D + i] = qv;
-            ks[tt * D + i] = kv;
-            if constexpr (DELTA) {
-                const float step = softplus_f(a[row * ((size_t)H * D) + (size_t)h * D + i] + dt_bias[(size_t)h * D + i]);
-                gs[tt * D + i] = expf(-rate * step);
+    auto fetch = [&](int which, int t0) {             // tokens t0 .. of the segment into buffer `which`
+        const int m = min(stage, n - t0);
+        float* qs = smem + which * buffer;
+        float* ks = qs + stage * Dp;
+        float* gs = ks + stage * Dp;
+        float* vs = qs + vectors * stage * Dp;
+        float* bs = vs + stage * COLS;
+        if ((D & 3) == 0) {                           // 16 bytes a copy: a slice's rows are a multiple of four
+            const int D4 = D >> 2;
+            for (int e = tid; e < m * D4; e += THREADS) {
+                const int tt = e / D4, i = (e - tt * D4) * 4;
+                const size_t row = (size_t)(q0 + t0 + tt);
+                const int at = tt * Dp + (i / per) * ps + i % per;
+                copy_async_16(qs + at, qf + (row * G + kh) * D + i);
+                copy_async_16(ks + at, kf + (row * G + kh) * D + i);
+                if constexpr (DELTA) copy_async_16(gs + at, gf + (row * H + h) * D + i);
+            }
+        } else {
+            for (int e = tid; e < m * D; e += THREADS) {
+                const int tt = e / D, i = e - tt * D;
+                const size_t row = (size_t)(q0 + t0 + tt);
+                const int at = tt * Dp + (i / per) * ps + i % per;
+                copy_async_4(qs + at, qf + (row * G + kh) * D + i);
+                copy_async_4(ks + at, kf + (row * G + kh) * D + i);
+                if constexpr (DELTA) copy_async_4(gs + at, gf + (row * H + h) * D + i);
             }
         }
-        for (int e = tid; e < m * 32; e += nthreads) {
-            const int tt = e >> 5, j = e & 31;
-            const int cj = blockIdx.x * 32 + j;
-            float vv = cj < V ? to_float(v[(size_t)(q0 + t0 + tt) * ld + (size_t)h * V + cj]) : 0.f;
-            if (silu_inputs) vv = silu_f<true>(vv);
-            vs[e] = vv;
+        for (int e = tid; e < m * COLS; e += THREADS) {
+            const int tt = e / COLS, j = e - tt * COLS;
+            if (col0 + j < V) copy_async_4(vs + e, vf + ((size_t)(q0 + t0 + tt) * H + h) * V + col0 + j);
         }
-        if constexpr (DELTA) {
-            if (tid < m) bs[tid] = 1.f / (1.f + expf(-to_float(b[(size_t)(q0 + t0 + tid) * ldb + h])));
-            __syncthreads();
-            // unit length per head: a warp a token
-            for (int tt = slice; tt < m; tt += DS) {
-                float sq = 0.f, sk = 0.f;
-                for (int i = lane; i < D; i += 32) {
-                    sq = fmaf(qs[tt * D + i], qs[tt * D + i], sq);
-                    sk = fmaf(ks[tt * D + i], ks[tt * D + i], sk);
-                }
-                sq = warp_sum(sq); sk = warp_sum(sk);
-                const float fq = q_scale / sqrtf(sq + 1e-6f), fk = 1.f / sqrtf(sk + 1e-6f);
-                for (int i = lane; i < D; i += 32) { qs[tt * D + i] *= fq; ks[tt * D + i] *= fk; }
-            }
-        }
-        __syncthreads();
+        if constexpr (DELTA)
+            if (tid < m) copy_async_4(bs + tid, bf + (size_t)(q0 + t0 + tid) * H + h);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    fetch(0, 0);
+    int which = 0;
+    for (int t0 = 0; t0 < n; t0 += stage, which ^= 1) {
+        const int m = min(stage, n - t0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                              // these tokens are here; the other buffer has been walked
+        if (t0 + stage < n) fetch(which ^ 1, t0 + stage);
+        const float* qs = smem + which * buffer + r * ps;
+        const float* ks = qs + stage * Dp;
+        const float* gs = ks + stage * Dp;
+        const float* vs = smem + which * buffer + vectors * stage * Dp + warp * C + c;
+        const float* bs = smem + which * buffer + vectors * stage * Dp + stage * COLS;
+#pragma unroll 2
         for (int tt = 0; tt < m; ++tt) {
-            const float* qt = qs + tt * D + row0;
-            const float* kt = ks + tt * D + row0;
-            const float vv = vs[tt * 32 + lane];
-            float o = 0.f;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * Dp);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * Dp);
+            const float vv = live ? vs[tt * COLS] : 0.f;
+            float o0 = 0.f, o1 = 0.f;
             if constexpr (DELTA) {
-                const float* gt = gs + tt * D + row0;
-                float kv = 0.f;
+                const float4* g4 = reinterpret_cast<const float4*>(gs + tt * Dp);
+                float kq[SCAN_ROWS];
+                float k0 = 0.f, k1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < DPT; ++i)
-                    if (row0 + i < D) { S[i] *= gt[i]; kv = fmaf(S[i], kt[i], kv); }
-                if (DS > 1) {
-                    red[slice * 32 + lane] = kv;
-                    __syncthreads();
-                    kv = 0.f;
-                    for (int r = 0; r < DS; ++r) kv += red[r * 32 + lane];
-                    __syncthreads();
+                for (int j = 0; j < SCAN_ROWS / 4; ++j) {
+                    if (4 * j < mine) {
+                        const float4 kv = k4[j], gv = g4[j];
+                        kq[4 * j] = kv.x; kq[4 * j + 1] = kv.y; kq[4 * j + 2] = kv.z; kq[4 * j + 3] = kv.w;
+                        if (4 * j < mine) { S[4 * j] *= gv.x; k0 = fmaf(S[4 * j], kv.x, k0); }
+                        if (4 * j + 1 < mine) { S[4 * j + 1] *= gv.y; k1 = fmaf(S[4 * j + 1], kv.y, k1); }
+                        if (4 * j + 2 < mine) { S[4 * j + 2] *= gv.z; k0 = fmaf(S[4 * j + 2], kv.z, k0); }
+                        if (4 * j + 3 < mine) { S[4 * j + 3] *= gv.w; k1 = fmaf(S[4 * j + 3], kv.w, k1); }
+                    }
                 }
-                const float u = bs[tt] * (vv - kv);
+                const float u = bs[tt] * (vv - slices_sum<R>(k0 + k1));
 #pragma unroll
-                for (int i = 0; i < DPT; ++i)
-                    if (row0 + i < D) { S[i] = fmaf(kt[i], u, S[i]); o = fmaf(S[i], qt[i], o); }
+                for (int j = 0; j < SCAN_ROWS / 4; ++j) {
+                    if (4 * j < mine) {
+                        const float4 qv = q4[j];
+                        if (4 * j < mine) { S[4 * j] = fmaf(kq[4 * j], u, S[4 * j]); o0 = fmaf(S[4 * j], qv.x, o0); }
+                        if (4 * j + 1 < mine) { S[4 * j + 1] = fmaf(kq[4 * j + 1], u, S[4 * j + 1]); o1 = fmaf(S[4 * j + 1], qv.y, o1); }
+                        if (4 * j + 2 < mine) { S[4 * j + 2] = fmaf(kq[4 * j + 2], u, S[4 * j + 2]); o0 = fmaf(S[4 * j + 2], qv.z, o0); }
+                        if (4 * j + 3 < mine) { S[4 * j + 3] = fmaf(kq[4 * j + 3], u, S[4 * j + 3]); o1 = fmaf(S[4 * j + 3], qv.w, o1); }
+                    }
+                }
             } else {
 #pragma unroll
-                for (int i = 0; i < DPT; ++i)
-                    if (row0 + i < D) { S[i] = fmaf(head_decay, S[i], kt[i] * vv); o = fmaf(S[i], qt[i], o); }
+                for (int j = 0; j < SCAN_ROWS / 4; ++j) {
+                    if (4 * j < mine) {
+                        const float4 kv = k4[j], qv = q4[j];
+                        if (4 * j < mine) { S[4 * j] = fmaf(head_decay, S[4 * j], kv.x * vv); o0 = fmaf(S[4 * j], qv.x, o0); }
+                        if (4 * j + 1 < mine) { S[4 * j + 1] = fmaf(head_decay, S[4 * j + 1], kv.y * vv); o1 = fmaf(S[4 * j + 1], qv.y, o1); }
+                        if (4 * j + 2 < mine) { S[4 * j + 2] = fmaf(head_decay, S[4 * j + 2], kv.z * vv); o0 = fmaf(S[4 * j + 2], qv.z, o0); }
+                        if (4 * j + 3 < mine) { S[4 * j + 3] = fmaf(head_decay, S[4 * j + 3], kv.w * vv); o1 = fmaf(S[4 * j + 3], qv.w, o1); }
+                    }
+                }
             }
-            if (DS > 1) {
-                red[slice * 32 + lane] = o;
-                __syncthreads();
-                o = 0.f;
-                for (int r = 0; r < DS; ++r) o += red[r * 32 + lane];
-                __syncthreads();
-            }
-            if (live && slice == 0) out[(size_t)(q0 + t0 + tt) * ((size_t)H * V) + (size_t)h * V + col] = o;
+            const float o = slices_sum<R>(o0 + o1);
+            if (live && r == 0) out[(size_t)(q0 + t0 + tt) * ((size_t)H * V) + (size_t)h * V + col] = o;
         }
     }
 #pragma unroll
-    for (int i = 0; i < DPT; ++i)
-        if (live && row0 + i < D) st[(size_t)(row0 + i) * V] = S[i];
+    for (int i = 0; i < SCAN_ROWS; ++i)
+        if (live && i < mine) st[(size_t)(row0 + i) * V] = S[i];
 }
 
 // A warp a (token, group).
@@ -233,21 +322,39 @@ gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ w, int 
     }
 }
 
+// scratch: float32, scan_scratch_floats() of them.
 template <typename TA, bool DELTA>
 int launch_scan(const void* q, const void* k, const void* v, long ld, int group, const float* a, const void* b,
                 long ldb, const float* a_log, const float* dt_bias, const float* decay, float* state, float* out,
-                const int* seg_q_start, const int* seg_slot, int segments, int H, int D, int V, int silu_inputs,
-                cudaStream_t stream) {
-    const int dpt = D <= 32 ? 32 : D <= 64 ? 64 : 128;
-    const int DS = (D + dpt - 1) / dpt;
-    const dim3 grid((V + 31) / 32, H, segments), block(32, DS);
-    const size_t smem = sizeof(float) * ((size_t)SCAN_TOKENS * D * (DELTA ? 3 : 2) + SCAN_TOKENS * 33 + DS * 32);
-#define MRUN_SCAN(DPT)                                                                                        \
-    scan_kernel<TA, DPT, DELTA><<<grid, block, smem, stream>>>((const TA*)q, (const TA*)k, (const TA*)v, ld,  \
-        group, a, (const TA*)b, ldb, a_log, dt_bias, decay, state, out, seg_q_start, seg_slot, H, D, V, silu_inputs)
-    if (dpt == 32) MRUN_SCAN(32);
-    else if (dpt == 64) MRUN_SCAN(64);
-    else MRUN_SCAN(128);
+                float* scratch, const int* seg_q_start, const int* seg_slot, int segments, int tokens, int H, int D,
+                int V, int silu_inputs, cudaStream_t stream) {
+    const int G = H / group;
+    float* qf = scratch;
+    float* kf = qf + (size_t)tokens * G * D;
+    float* gf = kf + (size_t)tokens * G * D;          // the three that are copied 16 bytes at a time first
+    float* vf = gf + (DELTA ? (size_t)tokens * H * D : 0);
+    float* bf = vf + (size_t)tokens * H * V;
+    scan_prepare_kernel<TA><<<tokens, 256, 0, stream>>>((const TA*)q, (const TA*)k, (const TA*)v, ld, a, (const TA*)b, ldb,
+                                                       a_log, dt_bias, qf, kf, gf, vf, bf, G, H, D, V, DELTA ? 1 : 0,
+                                                       silu_inputs);
+    const int R = D <= 16 ? 1 : D <= 32 ? 2 : D <= 64 ? 4 : D <= 128 ? 8 : 16;   // row slices: at most 16 rows a lane
+    const int cols = SCAN_WARPS * (32 / R);
+    const int per = (((D + R - 1) / R) + 3) & ~3;
+    const int stage = D <= 128 ? 16 : 8;
+    const dim3 grid((V + cols - 1) / cols, H, segments);
+    const size_t smem = sizeof(float) * 2 * ((size_t)stage * ((DELTA ? 3 : 2) * R * (per + 4) + cols) + stage);
+#define MRUN_SCAN(SLICES)                                                                                          \
+    do {                                                                                                           \
+        if (smem > 48 * 1024)                                                                                      \
+            cudaFuncSetAttribute(scan_kernel<SLICES, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        scan_kernel<SLICES, DELTA><<<grid, SCAN_WARPS * 32, smem, stream>>>(qf, kf, gf, vf, bf, decay, state, out, \
+                                                                            seg_q_start, seg_slot, group, G, H, D, V, stage); \
+    } while (0)
+    if (R == 1) MRUN_SCAN(1);
+    else if (R == 2) MRUN_SCAN(2);
+    else if (R == 4) MRUN_SCAN(4);
+    else if (R == 8) MRUN_SCAN(8);
+    else MRUN_SCAN(16);
 #undef MRUN_SCAN
     return 0;
 }
@@ -281,20 +388,25 @@ MRUN_API int mrun_causal_conv(const void* x, long ldx, const float* w, void* sta
 }
 
 // q, k: row t at + t * ld, [H / group heads, D]; v: [H, V] likewise.  state: float32 [slots, H, D, V];
-// out: float32 [tokens, H * V].  decay: float32 [H].
+// out: float32 [tokens, H * V].  decay: float32 [H].  scratch: float32, mrun_scan_scratch_floats() of them
+// (the prepared rows; a token's row of the batch is its row there, padding rows included).
+MRUN_API long mrun_scan_scratch_floats(int tokens, int H, int G, int D, int V, int delta) {
+    return (long)tokens * (2L * G * D + (long)H * V + (delta ? (long)H * D + H : 0));
+}
+
 MRUN_API int mrun_decay_scan(const void* q, const void* k, const void* v, long ld, int act_dtype, const float* decay,
-                             float* state, float* out, const int* seg_q_start, const int* seg_slot, int segments,
-                             int H, int D, int V, int silu_inputs, cudaStream_t stream) {
+                             float* state, float* out, float* scratch, const int* seg_q_start, const int* seg_slot,
+                             int segments, int tokens, int H, int D, int V, int silu_inputs, cudaStream_t stream) {
     MRUN_REQUIRE(H > 0 && D > 0 && V > 0 && segments >= 0, "decay_scan: bad sizes");
     MRUN_REQUIRE(D <= 256, "decay_scan: key size %d exceeds the supported 256", D);
     MRUN_REQUIRE(H <= 65535 && segments <= 65535, "decay_scan: %d heads or %d segments exceed 65535", H, segments);
-    if (segments == 0) return 0;
+    if (segments == 0 || tokens == 0) return 0;
     if (act_dtype == MRUN_F32)
-        launch_scan<float, false>(q, k, v, ld, 1, nullptr, nullptr, 0, nullptr, nullptr, decay, state, out, seg_q_start,
-                                  seg_slot, segments, H, D, V, silu_inputs, stream);
+        launch_scan<float, false>(q, k, v, ld, 1, nullptr, nullptr, 0, nullptr, nullptr, decay, state, out, scratch,
+                                  seg_q_start, seg_slot, segments, tokens, H, D, V, silu_inputs, stream);
     else if (act_dtype == MRUN_BF16)
         launch_scan<__nv_bfloat16, false>(q, k, v, ld, 1, nullptr, nullptr, 0, nullptr, nullptr, decay, state, out,
-                                          seg_q_start, seg_slot, segments, H, D, V, silu_inputs, stream);
+                                          scratch, seg_q_start, seg_slot, segments, tokens, H, D, V, silu_inputs, stream);
     else
         return mrun_set_error("decay_scan: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("decay_scan");
@@ -305,18 +417,18 @@ MRUN_API int mrun_decay_scan(const void* q, const void* k, const void* v, long l
 // b: row t at b + t * ldb, [H]; a_log: float32 [H]; dt_bias: float32 [H * D].
 MRUN_API int mrun_delta_scan(const void* q, const void* k, const void* v, long ld, int act_dtype, int group,
                              const float* a, const void* b, long ldb, const float* a_log, const float* dt_bias,
-                             float* state, float* out, const int* seg_q_start, const int* seg_slot, int segments,
-                             int H, int D, int V, cudaStream_t stream) {
+                             float* state, float* out, float* scratch, const int* seg_q_start, const int* seg_slot,
+                             int segments, int tokens, int H, int D, int V, cudaStream_t stream) {
     MRUN_REQUIRE(H > 0 && D > 0 && V > 0 && segments >= 0 && group > 0 && H % group == 0, "delta_scan: bad sizes");
     MRUN_REQUIRE(D <= 256, "delta_scan: key size %d exceeds the supported 256", D);
     MRUN_REQUIRE(H <= 65535 && segments <= 65535, "delta_scan: %d heads or %d segments exceed 65535", H, segments);
-    if (segments == 0) return 0;
+    if (segments == 0 || tokens == 0) return 0;
     if (act_dtype == MRUN_F32)
-        launch_scan<float, true>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out, seg_q_start,
-                                 seg_slot, segments, H, D, V, 0, stream);
+        launch_scan<float, true>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out, scratch,
+                                 seg_q_start, seg_slot, segments, tokens, H, D, V, 0, stream);
     else if (act_dtype == MRUN_BF16)
-        launch_scan<__nv_bfloat16, true>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out,
-                                         seg_q_start, seg_slot, segments, H, D, V, 0, stream);
+        launch_scan<__nv_bfloat16, true>(q, k, v, ld, group, a, b, ldb, a_log, dt_bias, nullptr, state, out, scratch,
+                                         seg_q_start, seg_slot, segments, tokens, H, D, V, 0, stream);
     else
         return mrun_set_error("delta_scan: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("delta_scan");

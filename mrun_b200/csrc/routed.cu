@@ -167,6 +167,32 @@ __global__ void clamped_glu_kernel(const TA* __restrict__ u, TA* __restrict__ ac
     act[i] = from_float<TA>(g * s * (up + 1.f) * w);
 }
 
+// Eight outputs a thread (ff a multiple of 8, 16-byte aligned rows): grid.x walks the rows, grid.y the chunks.
+template <typename TA, bool EXACT>
+__global__ void __launch_bounds__(256)
+clamped_glu_vec_kernel(const TA* __restrict__ u, TA* __restrict__ act, const float* __restrict__ weights, int per_block,
+                       int blocks, int ff, float limit, float alpha) {
+    const long row = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= blocks * ff) return;
+    const int e = c / ff, j = c - e * ff;
+    const TA* base = u + (row * blocks + e) * 2 * ff;
+    float g[8], up[8];
+    Vec8<TA>::load(base + j, g);
+    Vec8<TA>::load(base + ff + j, up);
+    const float w = weights ? (per_block ? weights[row * blocks + e] : weights[row]) : 1.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float gv = fminf(g[i], limit);
+        const float uv = fminf(fmaxf(up[i], -limit), limit);
+        float s;
+        if constexpr (EXACT) s = 1.f / (1.f + expf(-alpha * gv));
+        else s = __fdividef(1.f, 1.f + __expf(-alpha * gv));
+        g[i] = gv * s * (uv + 1.f) * w;
+    }
+    Vec8<TA>::store(act + row * blocks * ff + c, g);
+}
+
 }  // namespace
 
 MRUN_API int mrun_table_route(const int* ids, const int* table, float* weights, int* chosen, int tokens, int vocab,
@@ -185,6 +211,19 @@ MRUN_API int mrun_clamped_glu(const void* u, void* act, int act_dtype, const flo
     if (rows == 0) return 0;
     const long total = (long)rows * blocks * ff;
     const unsigned grid = (unsigned)((total + 255) / 256);
+    if (ff % 8 == 0 && ((((uintptr_t)u) | ((uintptr_t)act)) & 15) == 0 && rows <= 0x7fffffff) {
+        const dim3 vec_grid(rows, (blocks * ff / 8 + 255) / 256);
+        if (act_dtype == MRUN_F32)
+            clamped_glu_vec_kernel<float, true><<<vec_grid, 256, 0, stream>>>((const float*)u, (float*)act, weights,
+                                                                               per_block, blocks, ff, limit, alpha);
+        else if (act_dtype == MRUN_BF16)
+            clamped_glu_vec_kernel<__nv_bfloat16, false><<<vec_grid, 256, 0, stream>>>(
+                (const __nv_bfloat16*)u, (__nv_bfloat16*)act, weights, per_block, blocks, ff, limit, alpha);
+        else
+            return mrun_set_error("clamped_glu: unknown dtype code %d", act_dtype);
+        MRUN_CHECK_LAUNCH("clamped_glu");
+        return 0;
+    }
     if (act_dtype == MRUN_F32)
         clamped_glu_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)u, (float*)act, weights, per_block, total,
                                                                    blocks, ff, limit, alpha);

@@ -918,9 +918,11 @@ def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.T
             or state.shape[1:] != (heads, dim, vdim) or decay.numel() != heads:
         raise KernelError("decay_scan: sizes do not match")
     out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
+    scratch = torch.empty(tokens * (2 * heads * dim + heads * vdim), dtype=torch.float32, device=q.device)
     _lib.core().call("mrun_decay_scan", _ptr(q), _ptr(k), _ptr(v), _c_long(ld), dtype_code(q.dtype), _ptr(decay),
-                     _ptr(state), _ptr(out), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), _c_int(ctx.num_segments),
-                     _c_int(heads), _c_int(dim), _c_int(vdim), _c_int(1 if silu_inputs else 0), _stream())
+                     _ptr(state), _ptr(out), _ptr(scratch), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot),
+                     _c_int(ctx.num_segments), _c_int(tokens), _c_int(heads), _c_int(dim), _c_int(vdim),
+                     _c_int(1 if silu_inputs else 0), _stream())
     return out
 
 
@@ -943,10 +945,11 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tenso
             or a_log.numel() != heads or dt_bias.numel() != heads * dim or state.shape[1:] != (heads, dim, vdim):
         raise KernelError("delta_scan: sizes do not match")
     out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
+    scratch = torch.empty(tokens * (2 * kv_heads * dim + heads * (vdim + dim + 1)), dtype=torch.float32, device=q.device)
     _lib.core().call("mrun_delta_scan", _ptr(q), _ptr(k), _ptr(v), _c_long(ld), dtype_code(q.dtype),
                      _c_int(heads // kv_heads), _ptr(a), _ptr(b), _c_long(ldb), _ptr(a_log), _ptr(dt_bias), _ptr(state),
-                     _ptr(out), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), _c_int(ctx.num_segments), _c_int(heads),
-                     _c_int(dim), _c_int(vdim), _stream())
+                     _ptr(out), _ptr(scratch), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), _c_int(ctx.num_segments),
+                     _c_int(tokens), _c_int(heads), _c_int(dim), _c_int(vdim), _stream())
     return out
 
 

@@ -14,6 +14,7 @@ lambda is one number a layer and is computed from its four vectors when the weig
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -23,7 +24,9 @@ from ..kernels import ops
 from ..kernels.attention import paged_attention, supports_tensor_cores
 from .base import POSITIONS, Runtime, register_mixer
 
-TENSOR_CORE_MAPS = True      # False: the one-kernel CUDA-core path for every step (tests compare the two)
+# False (``MRUN_DIFF_TENSOR_CORE=0`` in the environment): the one-kernel CUDA-core path for every
+# step; the tests compare the two
+TENSOR_CORE_MAPS = os.environ.get("MRUN_DIFF_TENSOR_CORE", "1") != "0"
 
 
 class _MapCache:
