@@ -73,10 +73,11 @@ class DifferentialAttention:
         self.act = runtime.precision.act
         # value chunks of the key size let a (map, chunk) pair go through the kernels for equal
         # key and value sizes
-        self.chunks = 1
-        if (TENSOR_CORE_MAPS and self.act == torch.bfloat16 and V % D == 0
-                and supports_tensor_cores(self.act, D, H // G) and spec.window is None):
-            self.chunks = V // D
+        # (groups of more than 16 query heads would leave the decode kernels and need a tile list made
+        # on the host, which a captured decode step cannot have: they stay on the CUDA-core kernel)
+        self.tensor_core = (TENSOR_CORE_MAPS and self.act == torch.bfloat16 and V % D == 0 and H // G <= 16
+                            and supports_tensor_cores(self.act, D, H // G) and spec.window is None)
+        self.chunks = V // D if self.tensor_core else 1
 
     graph_safe = True
 
@@ -99,7 +100,7 @@ class DifferentialAttention:
                             H, G, D, V, self.page_size)
         out_scale = 1.0 - s.diff
         q = qkv[:, :2 * H * D]
-        if self.chunks == 1:
+        if not self.tensor_core:
             o = ops.diff_attention(q, cache.k, cache.v, group.block_tables, ctx.token_slot, ctx.positions, H, V,
                                    s.softmax_scale, self.lam, s.eps, out_scale, s.window or 0)
         else:

@@ -316,6 +316,8 @@ ATTENTION_SHAPES = [  # heads, kv heads, key size, value size, rotating features
     (4, 1, 12, 36, 0, 4),
     (4, 2, 64, 64, 16, 16),      # bfloat16: TMA decode and tcgen05 prefill kernels, one chunk
     (2, 1, 64, 128, 64, 8),      # the same, two chunks
+    (3, 1, 128, 128, 32, 16),    # the same kernels at 128
+    (34, 2, 16, 16, 4, 16),      # seventeen query heads a kv head: beyond the decode kernels' groups
 ]
 
 
