@@ -245,7 +245,7 @@ __device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int R, bool DELTA>
+template <int R, bool DELTA, bool FULL>
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const float* __restrict__ gf,
             const float* __restrict__ vf, const float* __restrict__ bf, const float* __restrict__ decay,
@@ -326,48 +326,40 @@ scan_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const fl
         for (int tt = 0; tt < m; ++tt) {
             const float4* q4 = reinterpret_cast<const float4*>(qs + tt * Dp);
             const float4* k4 = reinterpret_cast<const float4*>(ks + tt * Dp);
+            const float4* g4 = reinterpret_cast<const float4*>(gs + tt * Dp);
             const float vv = live ? vs[tt * COLS] : 0.f;
-            float o0 = 0.f, o1 = 0.f;
-            if constexpr (DELTA) {
-                const float4* g4 = reinterpret_cast<const float4*>(gs + tt * Dp);
-                float kq[SCAN_ROWS];
-                float k0 = 0.f, k1 = 0.f;
+            // the slice's rows of k, q (and g) of this token: FULL slices (every lane holds
+            // SCAN_ROWS rows) need no bound checks
+            float kr[SCAN_ROWS], qr[SCAN_ROWS], gr[SCAN_ROWS];
 #pragma unroll
-                for (int j = 0; j < SCAN_ROWS / 4; ++j) {
-                    if (4 * j < mine) {
-                        const float4 kv = k4[j], gv = g4[j];
-                        kq[4 * j] = kv.x; kq[4 * j + 1] = kv.y; kq[4 * j + 2] = kv.z; kq[4 * j + 3] = kv.w;
-                        if (4 * j < mine) { S[4 * j] *= gv.x; k0 = fmaf(S[4 * j], kv.x, k0); }
-                        if (4 * j + 1 < mine) { S[4 * j + 1] *= gv.y; k1 = fmaf(S[4 * j + 1], kv.y, k1); }
-                        if (4 * j + 2 < mine) { S[4 * j + 2] *= gv.z; k0 = fmaf(S[4 * j + 2], kv.z, k0); }
-                        if (4 * j + 3 < mine) { S[4 * j + 3] *= gv.w; k1 = fmaf(S[4 * j + 3], kv.w, k1); }
-                    }
-                }
-                const float u = bs[tt] * (vv - slices_sum<R>(k0 + k1));
-#pragma unroll
-                for (int j = 0; j < SCAN_ROWS / 4; ++j) {
-                    if (4 * j < mine) {
-                        const float4 qv = q4[j];
-                        if (4 * j < mine) { S[4 * j] = fmaf(kq[4 * j], u, S[4 * j]); o0 = fmaf(S[4 * j], qv.x, o0); }
-                        if (4 * j + 1 < mine) { S[4 * j + 1] = fmaf(kq[4 * j + 1], u, S[4 * j + 1]); o1 = fmaf(S[4 * j + 1], qv.y, o1); }
-                        if (4 * j + 2 < mine) { S[4 * j + 2] = fmaf(kq[4 * j + 2], u, S[4 * j + 2]); o0 = fmaf(S[4 * j + 2], qv.z, o0); }
-                        if (4 * j + 3 < mine) { S[4 * j + 3] = fmaf(kq[4 * j + 3], u, S[4 * j + 3]); o1 = fmaf(S[4 * j + 3], qv.w, o1); }
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < SCAN_ROWS / 4; ++j) {
-                    if (4 * j < mine) {
-                        const float4 kv = k4[j], qv = q4[j];
-                        if (4 * j < mine) { S[4 * j] = fmaf(head_decay, S[4 * j], kv.x * vv); o0 = fmaf(S[4 * j], qv.x, o0); }
-                        if (4 * j + 1 < mine) { S[4 * j + 1] = fmaf(head_decay, S[4 * j + 1], kv.y * vv); o1 = fmaf(S[4 * j + 1], qv.y, o1); }
-                        if (4 * j + 2 < mine) { S[4 * j + 2] = fmaf(head_decay, S[4 * j + 2], kv.z * vv); o0 = fmaf(S[4 * j + 2], qv.z, o0); }
-                        if (4 * j + 3 < mine) { S[4 * j + 3] = fmaf(head_decay, S[4 * j + 3], kv.w * vv); o1 = fmaf(S[4 * j + 3], qv.w, o1); }
+            for (int j = 0; j < SCAN_ROWS / 4; ++j) {
+                if (FULL || 4 * j < mine) {
+                    const float4 kv = k4[j], qv = q4[j];
+                    kr[4 * j] = kv.x; kr[4 * j + 1] = kv.y; kr[4 * j + 2] = kv.z; kr[4 * j + 3] = kv.w;
+                    qr[4 * j] = qv.x; qr[4 * j + 1] = qv.y; qr[4 * j + 2] = qv.z; qr[4 * j + 3] = qv.w;
+                    if constexpr (DELTA) {
+                        const float4 gv = g4[j];
+                        gr[4 * j] = gv.x; gr[4 * j + 1] = gv.y; gr[4 * j + 2] = gv.z; gr[4 * j + 3] = gv.w;
                     }
                 }
             }
-            const float o = slices_sum<R>(o0 + o1);
-            if (live && r == 0) out[(size_t)(q0 + t0 + tt) * ((size_t)H * V) + (size_t)h * V + col] = o;
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (DELTA) {
+                float kd[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < SCAN_ROWS; ++i)
+                    if (FULL || i < mine) { S[i] *= gr[i]; kd[i & 3] = fmaf(S[i], kr[i], kd[i & 3]); }
+                const float u = bs[tt] * (vv - slices_sum<R>((kd[0] + kd[1]) + (kd[2] + kd[3])));
+#pragma unroll
+                for (int i = 0; i < SCAN_ROWS; ++i)
+                    if (FULL || i < mine) { S[i] = fmaf(kr[i], u, S[i]); o[i & 3] = fmaf(S[i], qr[i], o[i & 3]); }
+            } else {
+#pragma unroll
+                for (int i = 0; i < SCAN_ROWS; ++i)
+                    if (FULL || i < mine) { S[i] = fmaf(head_decay, S[i], kr[i] * vv); o[i & 3] = fmaf(S[i], qr[i], o[i & 3]); }
+            }
+            const float total = slices_sum<R>((o[0] + o[1]) + (o[2] + o[3]));
+            if (live && r == 0) out[(size_t)(q0 + t0 + tt) * ((size_t)H * V) + (size_t)h * V + col] = total;
         }
     }
 #pragma unroll
@@ -418,18 +410,25 @@ int launch_scan(const void* q, const void* k, const void* v, long ld, int group,
     const int stage = D <= 128 ? 16 : 8;
     const dim3 grid((V + cols - 1) / cols, H, segments);
     const size_t smem = sizeof(float) * 2 * ((size_t)stage * ((DELTA ? 3 : 2) * R * (per + 4) + cols) + stage);
-#define MRUN_SCAN(SLICES)                                                                                          \
+#define MRUN_SCAN_AS(SLICES, WHOLE)                                                                                 \
     do {                                                                                                           \
         if (smem > 48 * 1024)                                                                                      \
-            cudaFuncSetAttribute(scan_kernel<SLICES, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        scan_kernel<SLICES, DELTA><<<grid, SCAN_WARPS * 32, smem, stream>>>(qf, kf, gf, vf, bf, decay, state, out, \
-                                                                            seg_q_start, seg_slot, group, G, H, D, V, stage); \
+            cudaFuncSetAttribute(scan_kernel<SLICES, DELTA, WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                 (int)smem);                                                                       \
+        scan_kernel<SLICES, DELTA, WHOLE><<<grid, SCAN_WARPS * 32, smem, stream>>>(                                \
+            qf, kf, gf, vf, bf, decay, state, out, seg_q_start, seg_slot, group, G, H, D, V, stage);               \
+    } while (0)
+#define MRUN_SCAN(SLICES)                                                                                          \
+    do {                                                                                                           \
+        if (D == SLICES * SCAN_ROWS) MRUN_SCAN_AS(SLICES, true);          /* every lane holds SCAN_ROWS rows */   \
+        else MRUN_SCAN_AS(SLICES, false);                                                                          \
     } while (0)
     if (R == 1) MRUN_SCAN(1);
     else if (R == 2) MRUN_SCAN(2);
     else if (R == 4) MRUN_SCAN(4);
     else if (R == 8) MRUN_SCAN(8);
     else MRUN_SCAN(16);
+#undef MRUN_SCAN_AS
 #undef MRUN_SCAN
     return 0;
 }
