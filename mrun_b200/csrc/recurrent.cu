@@ -390,6 +390,28 @@ gated_norm_kernel(const float* __restrict__ o, const float* __restrict__ w, int 
 }
 
 // scratch: float32, scan_scratch_floats() of them.
+// A block a (token, group), for groups of many features.  The sums differ from the warp kernel's in
+// their order; which of the two runs depends on the group's size only.
+template <typename TA>
+__global__ void __launch_bounds__(256)
+gated_norm_block_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_len, const TA* __restrict__ gate,
+                        long ldg, float eps, TA* __restrict__ out, int groups, int n) {
+    __shared__ float scratch[33];
+    const long pair = blockIdx.x;
+    const long t = pair / groups;
+    const int g = (int)(pair - t * groups);
+    const float* row = o + (t * groups + g) * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) ss = fmaf(row[i], row[i], ss);
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const int c = g * n + i;
+        const float gv = to_float(gate[t * ldg + c]);
+        out[(t * groups + g) * n + i] = from_float<TA>(row[i] * inv * w[c % w_len] * (1.f / (1.f + expf(-gv))));
+    }
+}
+
 template <typename TA, bool DELTA>
 int launch_scan(const void* q, const void* k, const void* v, long ld, int group, const float* a, const void* b,
                 long ldb, const float* a_log, const float* dt_bias, const float* decay, float* state, float* out,
@@ -535,6 +557,18 @@ MRUN_API int mrun_gated_norm(const float* o, const float* w, int w_len, const vo
     if (tokens == 0) return 0;
     const long pairs = (long)tokens * groups;
     const unsigned blocks = (unsigned)((pairs + 3) / 4);
+    if (n >= 1024) {            // a block a pair
+        if (act_dtype == MRUN_F32)
+            gated_norm_block_kernel<float><<<(unsigned)pairs, 256, 0, stream>>>(o, w, w_len, (const float*)gate, ldg, eps,
+                                                                                 (float*)out, groups, n);
+        else if (act_dtype == MRUN_BF16)
+            gated_norm_block_kernel<__nv_bfloat16><<<(unsigned)pairs, 256, 0, stream>>>(
+                o, w, w_len, (const __nv_bfloat16*)gate, ldg, eps, (__nv_bfloat16*)out, groups, n);
+        else
+            return mrun_set_error("gated_norm: unknown dtype code %d", act_dtype);
+        MRUN_CHECK_LAUNCH("gated_norm");
+        return 0;
+    }
     if (act_dtype == MRUN_F32)
         gated_norm_kernel<float><<<blocks, 128, 0, stream>>>(o, w, w_len, (const float*)gate, ldg, eps, (float*)out,
                                                               pairs, groups, n);

@@ -223,7 +223,7 @@ def test_gated_norm_kernel(dtype):
     from mrun_b200.kernels import ops
     act = torch.float32 if dtype == "float32" else torch.bfloat16
     gen = torch.Generator().manual_seed(8)
-    for groups, n, shared in ((1, 120, False), (6, 20, True), (3, 33, True), (4, 128, False)):
+    for groups, n, shared in ((1, 120, False), (6, 20, True), (3, 33, True), (4, 128, False), (1, 2050, False), (2, 1024, True)):
         o = (torch.randn(9, groups * n, generator=gen) * 3).to(DEV)
         wide = torch.randn(9, groups * n + 16, generator=gen).to(DEV, act)
         gate = wide[:, 16:]
