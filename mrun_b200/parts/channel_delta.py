@@ -76,8 +76,8 @@ class ChannelDelta:
         b = y[:, at:at + s.heads]; at += s.heads
         a1 = y[:, at:at + s.decay_rank]; at += s.decay_rank
         g1 = y[:, at:at + s.gate_rank]
-        a = ops.linear(a1.contiguous(), self.w_a2, out_dtype=torch.float32)
-        gate = ops.linear(g1.contiguous(), self.w_g2)
+        a = ops.linear(a1, self.w_a2, out_dtype=torch.float32)          # column slices: the products take row strides
+        gate = ops.linear(g1, self.w_g2)
         qkv = ops.causal_conv(y[:, :C], self.conv_weight, cache.states["conv"], ctx, residual=False, silu=True)
         o = ops.delta_scan(qkv[:, :qk], qkv[:, qk:2 * qk], qkv[:, 2 * qk:], a, b, self.a_log, self.dt_bias,
                            cache.states["state"], ctx, s.heads, s.kv_heads, s.dim, s.vdim)

@@ -597,7 +597,7 @@ def test_preempted_requests_start_from_a_cleared_state(tmp_path):
     and its state slot back and is fed again from its first token; its recurrent and convolution
     states must then start from zero, or its later tokens differ from a run with room enough."""
     from mrun_b200 import Engine
-    folder = make_folder("X", str(tmp_path / "x"))
+    folder = make_folder("U", str(tmp_path / "u"))          # attention layers (pages) beside both recurrent kinds
     cfg, weights = load_folder(folder)
     prompts = [tokens_of(cfg["vocab"], n, seed=400 + n) for n in (20, 25, 30, 18)]
     roomy = Engine.from_folder(folder, dtype="float32", page_size=16, context=1024, max_batch_tokens=32, max_requests=4)
