@@ -16,6 +16,8 @@ batch 1, 8 and 32), and ``--serve`` times a mixed workload of 16 requests throug
 ``--design zasesun`` measures the Zasesun decoder (latent attention, sandwich norms, dense and
 routed feed-forwards) beside the Qwen3 decoder at equal widths, depths and head counts: prefill of
 2,048 tokens and decode at batch 8, each with its own FLOP and byte counts against the peaks.
+``--design balivik`` does the same for the Balivik decoder (differential attention, decay attention
+and a channel-wise delta rule under four residual streams, dense and table-routed feed-forwards).
 """
 from __future__ import annotations
 
