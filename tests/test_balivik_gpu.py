@@ -643,3 +643,49 @@ def test_command_line_random_then_run(tmp_path):
         assert token == best or float(logits[best] - logits[token]) < 1e-3
         tokens.append(token)
     assert len(tokens) == 19 + 6 and "Balivik" in result.stderr
+
+
+# ------------------------------------------------------------------ layer sizes of a real model
+
+REAL_SIZES = {"architecture": "Balivik", "vocab": 4096, "width": 1024, "norm": {"eps": 1e-6}, "streams": 4,
+              "canon": {"taps": 4}, "logit_scale": 0.5,
+              "layers": [
+                  {"type": "channel_delta", "mlp": {"kind": "dense", "ff": 2048},
+                   "mixer": {"heads": 8, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}},
+                  {"type": "attention", "mlp": {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": 512, "limit": 7.0}},
+                   "mixer": {"heads": 8, "kv_heads": 2, "dim": 128, "vdim": 256, "scale": 128 ** -0.5, "diff": 0.3,
+                             "rot": {"base": 10000.0, "dims": 64}}},
+                  {"type": "lightning", "mlp": {"kind": "dense", "ff": 2048},
+                   "mixer": {"heads": 8, "dim": 128, "vdim": 128, "decay": [1 - 2.0 ** -(2 + i) for i in range(8)]}}]}
+
+
+@pytest.mark.parametrize("dtype, sorted_experts", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_real_layer_sizes(dtype, sorted_experts, tmp_path, monkeypatch):
+    """Heads of 128 x 128 (full row slices of the scans), attention keys of 128 with values of 256
+    (two chunks through the tcgen05 and TMA kernels), four streams of 1,024, experts of 512: a
+    prompt whole and in portions, then decoded token by token, against the plain model."""
+    from mrun_b200.config.balivik import BalivikConfig
+    from mrun_b200.engine import StepEntry
+    from mrun_b200.engine.loading import executor_from_folder
+    from mrun_b200.parts import routed
+    from mrun_b200.weights import write_random_model
+    monkeypatch.setattr(routed, "SORT_MIN_SAVED_FLOPS", 0.0 if sorted_experts else 1e30)
+    folder = write_random_model(BalivikConfig.from_dict(REAL_SIZES), str(tmp_path / "real"), seed=7, std=0.03, norm_noise=0.1)
+    cfg, weights = load_folder(folder)
+    tokens = tokens_of(cfg["vocab"], 330, seed=77)
+    want = plain.forward(cfg, weights, tokens).to(torch.float32)
+    ex = executor_from_folder(folder, dtype=dtype, page_size=16, num_pages=64, max_requests=2)
+    seen = {}
+    for label, portions in (("whole", [330]), ("portions", [200, 3, 65, 30] + [1] * 32)):
+        request, at, got = ex.admit(label), 0, []
+        for n in portions:
+            got.append(ex.step([StepEntry(request, tokens[at:at + n], list(range(n)))]).cpu())
+            at += n
+        ex.release(request)
+        got = torch.cat(got)
+        error = float((got - want).abs().max() / want.abs().max())
+        print(dtype, sorted_experts, label, f"{error:.2e}")
+        assert error <= (2e-5 if dtype == "float32" else BF16_MODEL_BOUND), f"{label}: {error:.3e}"
+        if dtype == "float32":
+            assert torch.equal(seen.setdefault("logits", got), got), "the cuttings differ in bits"
+    ex.check()
