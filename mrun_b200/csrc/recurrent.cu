@@ -24,7 +24,7 @@ using namespace mrun;
 namespace {
 
 constexpr int MAX_TAPS = 8;
-constexpr int CONV_TILE = 8;        // tokens a block walks; at least MAX_TAPS - 1
+constexpr int CONV_TILE = 16;       // tokens a block walks; at least MAX_TAPS - 1 (measured: 8 is slower, every block loads its weights)
 
 template <bool EXACT> __device__ __forceinline__ float silu_f(float z) {
     if constexpr (EXACT) return z / (1.f + expf(-z));
