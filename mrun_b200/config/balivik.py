@@ -75,7 +75,8 @@ class BalivikConfig:
         m = _section(layer, "mixer", where)
         mw = f"{where}mixer."
         if kind == "attention":
-            heads, kv_heads = _count(m, "heads", mw), _count(m, "kv_heads", mw)
+            heads = _count(m, "heads", mw)
+            kv_heads = _count(m, "kv_heads", mw) if m.get("kv_heads") is not None else heads
             if heads % kv_heads:
                 raise ConfigError(f"{mw}heads", f"({heads}) is not a multiple of kv_heads ({kv_heads})")
             dim = _count(m, "dim", mw)
@@ -96,13 +97,16 @@ class BalivikConfig:
         if kind == "lightning":
             heads = _count(m, "heads", mw)
             decay = m.get("decay")
+            if isinstance(decay, (int, float)) and not isinstance(decay, bool):
+                decay = [decay] * heads             # one number for all heads
             if not isinstance(decay, list) or len(decay) != heads or \
                     any(isinstance(d, bool) or not isinstance(d, (int, float)) for d in decay):
                 raise ConfigError(f"{mw}decay", f"must list one number for each of the {heads} heads")
             return DecayAttentionSpec(hidden=width, heads=heads, dim=_count(m, "dim", mw), vdim=_count(m, "vdim", mw),
                                       decay=tuple(float(d) for d in decay), eps=eps)
         if kind == "channel_delta":
-            heads, kv_heads = _count(m, "heads", mw), _count(m, "kv_heads", mw)
+            heads = _count(m, "heads", mw)
+            kv_heads = _count(m, "kv_heads", mw) if m.get("kv_heads") is not None else heads
             if heads % kv_heads:
                 raise ConfigError(f"{mw}heads", f"({heads}) is not a multiple of kv_heads ({kv_heads})")
             ranks = {}
@@ -114,7 +118,7 @@ class BalivikConfig:
                 else:
                     raise ConfigError(f"{mw}{key}", f"is given neither by the checkpoint tensor {tensor} nor by the key")
             return ChannelDeltaSpec(hidden=width, heads=heads, kv_heads=kv_heads, dim=_count(m, "dim", mw),
-                                    vdim=_count(m, "vdim", mw), conv=_count(m, "conv", mw, 2), eps=eps, **ranks)
+                                    vdim=_count(m, "vdim", mw), conv=_count(m, "conv", mw), eps=eps, **ranks)
         raise ConfigError(f"{where}type", f"names the unknown mixer {kind!r}")
 
     @staticmethod
@@ -160,7 +164,7 @@ class BalivikConfig:
             raise ConfigError("streams", f"must be at most 8, got {streams}")
         taps = 0
         if cfg.get("canon") is not None:
-            taps = _count(_section(cfg, "canon", ""), "taps", "canon.", 2)
+            taps = _count(_section(cfg, "canon", ""), "taps", "canon.")
         loop = None
         if cfg.get("loop") is not None:
             section = _section(cfg, "loop", "")

@@ -463,7 +463,7 @@ MRUN_API int mrun_causal_conv(const void* x, long ldx, const float* w, void* sta
                               const int* seg_q_start, const int* seg_slot, int segments, int max_q_len, int C,
                               int taps, int residual, int silu, cudaStream_t stream) {
     MRUN_REQUIRE(C > 0 && segments >= 0 && max_q_len >= 0, "causal_conv: bad sizes");
-    MRUN_REQUIRE(taps >= 2 && taps <= MAX_TAPS, "causal_conv: %d taps, the kernel takes 2 to %d", taps, MAX_TAPS);
+    MRUN_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "causal_conv: %d taps, the kernel takes 1 to %d", taps, MAX_TAPS);
     MRUN_REQUIRE(ldx >= C && ldo >= C, "causal_conv: a row stride below the %d channels", C);
     MRUN_REQUIRE(segments <= 65535, "causal_conv: %d segments exceed 65535", segments);
     if (segments == 0 || max_q_len == 0) return 0;

@@ -883,7 +883,8 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, ctx,
     """Causal convolution per channel over each request's tokens (the last tap meets the token
     itself), added to x (``residual``) and/or passed through SiLU.  ``x``: [tokens, channels],
     rows may be strided; ``weight``: float32 [channels, taps]; ``state``: [slots, taps - 1,
-    channels] in x's dtype, the request's last inputs, read and left up to date."""
+    channels] in x's dtype, the request's last inputs, read and left up to date (empty with one
+    tap, which sees the token itself only)."""
     _check(x, "x", dense=False); _check(weight, "weight", torch.float32); _check(state, "state", x.dtype)
     tokens, channels = x.shape
     taps = weight.shape[1]

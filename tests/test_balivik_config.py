@@ -99,9 +99,23 @@ def test_refusals_name_the_key():
     refused(lambda c: c["layers"][1]["mlp"]["expert"].pop("limit"), "layers[1].mlp.expert.limit")
     refused(lambda c: c["layers"][0]["mlp"].update(kind="conv"), "layers[0].mlp.kind")
     refused(lambda c: c["loop"].update(stop=9), "loop")
-    refused(lambda c: c["canon"].update(taps=1), "canon.taps")
+    refused(lambda c: c["canon"].update(taps=0), "canon.taps")
     refused(lambda c: c.update(streams=9), "streams")
     refused(lambda c: c.pop("width"), "width")
+
+
+def test_defaults_of_keys_a_config_may_leave_out():
+    from mrun_b200.config.balivik import BalivikConfig
+    cfg = copy.deepcopy(BTINY["V"]["config"])
+    cfg["layers"][0]["mixer"].pop("kv_heads")               # as many key heads as heads
+    cfg["layers"][2]["mixer"].pop("kv_heads")
+    cfg["layers"][1]["mixer"]["decay"] = 0.9                # one decay for all heads
+    config = BalivikConfig.from_dict(cfg)
+    assert config.layers[0].mixer.kv_heads == 5 and config.layers[2].mixer.kv_heads == 2
+    assert config.layers[1].mixer.decay == (0.9, 0.9)
+    assert config.streams is None and config.canon_taps == 0 and config.loop is None and config.logit_scale is None
+    spec = config.to_spec()
+    assert spec.streams == 1 and spec.logits_transform is None and all(l.streams == 0 for l in spec.layers)
 
 
 def test_random_folder_and_ranks_from_the_checkpoint(tmp_path):

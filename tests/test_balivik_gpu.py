@@ -181,7 +181,8 @@ def test_streams_step_kernel(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("taps, channels, residual", [(2, 100, True), (4, 64, True), (3, 200, False), (8, 33, False)])
+@pytest.mark.parametrize("taps, channels, residual", [(2, 100, True), (4, 64, True), (3, 200, False), (8, 33, False),
+                                                      (1, 40, True), (1, 9, False)])
 def test_causal_conv_with_state(dtype, taps, channels, residual):
     """Requests fed in portions down to one token, side by side, with slots used again: every
     output equals the convolution over the whole request, zeros before its start."""
